@@ -1,0 +1,286 @@
+"""The ``cuda`` backend: thin Python wrappers over the sm_100a C-ABI library.
+
+Each wrapper has the name and keyword arguments of the reference's wrapper in
+comfy_kitchen/backends/cuda/__init__.py (quantize_nvfp4 :215-265, quantize_mxfp8
+:303-336, scaled_mm_nvfp4 :339-463), allocates the outputs with torch, and passes raw
+device pointers, sizes and the current stream through ``ctypes``.  Nothing here
+computes: if the library is missing the backend is marked unavailable and every
+operator raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from comfy_kitchen.float_utils import roundup
+from comfy_kitchen.ops import DTYPE_TO_CODE
+
+__all__ = [
+    "quantize_nvfp4",
+    "quantize_mxfp8",
+    "scaled_mm_nvfp4",
+    "scaled_mm_mxfp8",
+]
+
+_PKG_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+_DEFAULT_LIB = os.path.join(_PKG_ROOT, "lib", "libck_b200.so")
+ABI_VERSION = 1
+
+_lib = None
+_lib_error: str | None = None
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_int64
+
+# symbol -> argument types (return type is int unless listed in _RESTYPE)
+_SIGNATURES = {
+    "ck_abi_version": [],
+    "ck_last_error": [],
+    "ck_device_supported": [_I],
+    "ck_debug_set_exact_division": [_I],
+    "ck_quantize_nvfp4": [_P, _I, _P, _P, _P, _L, _L, _L, _L, _I, _P],
+    "ck_quantize_mxfp8": [_P, _I, _P, _P, _L, _L, _L, _L, _P],
+    "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
+    "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
+}
+_RESTYPE = {"ck_last_error": ctypes.c_char_p}
+
+
+def library_path() -> str:
+    """Path of the shared library: ``$CK_LIB`` if set, else ``lib/libck_b200.so`` next to the package."""
+    return os.environ.get("CK_LIB", _DEFAULT_LIB)
+
+
+def load_library():
+    """Load the C-ABI library once and declare its signatures.  Raises RuntimeError when it cannot."""
+    global _lib, _lib_error
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        _lib_error = f"C-ABI library not found at {path} (build it with comfy-kitchen_b200/build.py)"
+        raise RuntimeError(_lib_error)
+    try:
+        lib = ctypes.CDLL(path)
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _RESTYPE.get(name, _I)
+        got = lib.ck_abi_version()
+        if got != ABI_VERSION:
+            raise RuntimeError(f"ABI version {got} != expected {ABI_VERSION}")
+    except (OSError, AttributeError, RuntimeError) as e:
+        _lib_error = f"cannot load {path}: {e}"
+        raise RuntimeError(_lib_error) from e
+    _lib = lib
+    return lib
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = _lib.ck_last_error()
+        raise RuntimeError(f"{what} failed (code {rc}): {msg.decode() if msg else 'unknown error'}")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _plain(t):
+    return t.data if isinstance(t, torch.nn.Parameter) else t
+
+
+def _scalar_f32(t: torch.Tensor, device, what: str) -> torch.Tensor:
+    t = _plain(t)
+    if t.numel() != 1:
+        raise ValueError(f"{what} must hold exactly one value")
+    if t.dtype != torch.float32 or t.device != device:
+        t = t.to(device=device, dtype=torch.float32)
+    return t.reshape(1)
+
+
+# ------------------------------------------------------------------------------------------
+# quantizers
+# ------------------------------------------------------------------------------------------
+def quantize_nvfp4(x: torch.Tensor, per_tensor_scale: torch.Tensor, epsilon: float = 0.0, pad_16x: bool = False,
+                   hi_first: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16/f16/f32 [M, K] -> (uint8 [M', K'/2] codes, float8_e4m3fn swizzled block scales).
+
+    ``epsilon`` is accepted for signature compatibility and unused, as in the reference.
+    The scale tensor is allocated uninitialised: the kernel writes its padding as zeros.
+    """
+    lib = load_library()
+    x = _plain(x)
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    rows, cols = x.shape
+    if pad_16x:
+        out_rows, out_cols = roundup(rows, 16), roundup(cols, 16)
+    else:
+        # rows are unconstrained, as in the eager implementation the results are pinned to
+        out_rows, out_cols = rows, cols
+        assert out_cols % 16 == 0, f"num_cols must be divisible by 16, got {out_cols}"
+    scale = _scalar_f32(per_tensor_scale, x.device, "per_tensor_scale")
+    qx = torch.empty((out_rows, out_cols // 2), device=x.device, dtype=torch.uint8)
+    sx = torch.empty((roundup(out_rows, 128), roundup(out_cols // 16, 4)), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        _check(lib.ck_quantize_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(scale), _ptr(qx), _ptr(sx), rows, cols,
+                                     out_rows, out_cols, int(bool(hi_first)), _stream(x.device)), "quantize_nvfp4")
+    return qx, sx.view(torch.float8_e4m3fn)
+
+
+def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16/f16/f32 [M, K] -> (float8_e4m3fn [M', K'], float8_e8m0fnu swizzled block scales)."""
+    lib = load_library()
+    x = _plain(x)
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    rows, cols = x.shape
+    if pad_32x:
+        out_rows, out_cols = roundup(rows, 32), roundup(cols, 32)
+    else:
+        out_rows, out_cols = rows, cols
+        assert out_cols % 32 == 0, f"num_cols must be divisible by 32, got {out_cols}"
+    qx = torch.empty((out_rows, out_cols), device=x.device, dtype=torch.uint8)
+    sx = torch.empty((roundup(out_rows, 128), roundup(out_cols // 32, 4)), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        _check(lib.ck_quantize_mxfp8(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(qx), _ptr(sx), rows, cols, out_rows,
+                                     out_cols, _stream(x.device)), "quantize_mxfp8")
+    return qx.view(torch.float8_e4m3fn), sx.view(torch.float8_e8m0fnu)
+
+
+# ------------------------------------------------------------------------------------------
+# GEMMs
+# ------------------------------------------------------------------------------------------
+def _bias_args(bias, n: int, device):
+    if bias is None or bias.numel() == 0:
+        return None, 0, None
+    bias = _plain(bias)
+    assert bias.dtype in DTYPE_TO_CODE and DTYPE_TO_CODE[bias.dtype] <= 2, "bias must be f32, f16 or bf16"
+    assert bias.numel() == n, f"bias must have {n} elements"
+    bias = bias.contiguous()
+    if bias.device != device:
+        bias = bias.to(device)
+    return bias.data_ptr(), DTYPE_TO_CODE[bias.dtype], bias
+
+
+def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tensor, tensor_scale_b: torch.Tensor,
+                    block_scale_a: torch.Tensor, block_scale_b: torch.Tensor, bias: torch.Tensor | None = None,
+                    out_dtype: torch.dtype | None = None, alpha: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = (deq(a) @ deq(b).T) * (tensor_scale_a * tensor_scale_b) + bias.
+
+    a: uint8 [M, K/2], b: uint8 [N, K/2]; block scales in the swizzled layout.  ``alpha``
+    overrides the product of the tensor scales when given, as in the reference wrapper.
+    """
+    lib = load_library()
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    out_dtype = out_dtype or torch.bfloat16
+    m, ka = a.shape
+    n, kb = b.shape
+    assert ka == kb, "Matrix dimensions do not match"
+    k = 2 * ka
+    assert n % 8 == 0, "B tensor must have 8 alignment in N dimension"
+    assert block_scale_a.dtype == block_scale_b.dtype == torch.float8_e4m3fn, "NVFP4 block scales must be float8_e4m3fn"
+    sk = roundup(k // 16, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    assert a.is_contiguous() and b.is_contiguous() and block_scale_a.is_contiguous() and block_scale_b.is_contiguous()
+    dev = a.device
+    tsa = _scalar_f32(tensor_scale_a, dev, "tensor_scale_a")
+    tsb = _scalar_f32(tensor_scale_b, dev, "tensor_scale_b")
+    alpha_t = None if alpha is None else _scalar_f32(alpha, dev, "alpha")
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib.ck_scaled_mm_nvfp4(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa), _ptr(tsb),
+                                      _ptr(alpha_t), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
+                                      _stream(dev)), "scaled_mm_nvfp4")
+    del bias_keep
+    return out
+
+
+def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,
+                    bias: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """out[M, N] = deq(a) @ deq(b).T + bias with E4M3 data [M, K] / [N, K] and E8M0 1x32 block scales."""
+    lib = load_library()
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    out_dtype = out_dtype or torch.bfloat16
+    m, k = a.shape
+    n, kb = b.shape
+    assert k == kb, "Matrix dimensions do not match"
+    assert n % 8 == 0, "B tensor must have 8 alignment in N dimension"
+    sk = roundup(k // 32, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    assert a.is_contiguous() and b.is_contiguous() and block_scale_a.is_contiguous() and block_scale_b.is_contiguous()
+    dev = a.device
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib.ck_scaled_mm_mxfp8(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), bias_ptr, bias_code,
+                                      _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, _stream(dev)), "scaled_mm_mxfp8")
+    del bias_keep
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# registration
+# ------------------------------------------------------------------------------------------
+def _build_constraints() -> dict:
+    from comfy_kitchen.constraints import DivisibleBy, ExactDims, FunctionConstraints, ParamConstraint
+
+    cuda_only = frozenset({"cuda"})
+    floats = frozenset({torch.float32, torch.float16, torch.bfloat16})
+    f32 = frozenset({torch.float32})
+    blackwell = (10, 0)
+    return {
+        "quantize_nvfp4": FunctionConstraints(
+            params={"x": ParamConstraint(dtypes=floats, shape_rules=(ExactDims(2),)),
+                    "per_tensor_scale": ParamConstraint(dtypes=f32)},
+            default_devices=cuda_only, min_compute_capability=blackwell),
+        "quantize_mxfp8": FunctionConstraints(
+            params={"x": ParamConstraint(dtypes=floats, shape_rules=(ExactDims(2),))},
+            default_devices=cuda_only, min_compute_capability=blackwell),
+        "scaled_mm_nvfp4": FunctionConstraints(
+            params={"a": ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=(ExactDims(2), DivisibleBy(1, 16))),
+                    "b": ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=(ExactDims(2), DivisibleBy(1, 16))),
+                    "tensor_scale_a": ParamConstraint(dtypes=f32),
+                    "tensor_scale_b": ParamConstraint(dtypes=f32),
+                    "block_scale_a": ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn})),
+                    "block_scale_b": ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn})),
+                    "out_dtype": ParamConstraint(dtypes=floats)},
+            default_devices=cuda_only, min_compute_capability=blackwell),
+        "scaled_mm_mxfp8": FunctionConstraints(
+            params={"a": ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn}), shape_rules=(ExactDims(2), DivisibleBy(1, 32))),
+                    "b": ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn}), shape_rules=(ExactDims(2), DivisibleBy(1, 32))),
+                    "block_scale_a": ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                    "block_scale_b": ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                    "out_dtype": ParamConstraint(dtypes=floats)},
+            default_devices=cuda_only, min_compute_capability=blackwell),
+    }
+
+
+def _register():
+    import sys
+
+    from comfy_kitchen.registry import registry
+
+    try:
+        load_library()
+    except RuntimeError as e:
+        registry.mark_unavailable("cuda", str(e))
+        return
+    if not torch.cuda.is_available():
+        registry.mark_unavailable("cuda", "CUDA not available on this system")
+        return
+    registry.register("cuda", sys.modules[__name__], _build_constraints())
+
+
+_register()

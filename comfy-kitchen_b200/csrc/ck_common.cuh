@@ -1,0 +1,68 @@
+// Shared host/device helpers of the sm_100a quantized-linear library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+
+#include "../../include/ck_b200.h"
+
+namespace ck {
+
+// ---- error reporting --------------------------------------------------------
+// The message buffer is thread-local: the C entry points are re-entrant and a
+// failure on one thread never overwrites the message another thread reads.
+char* last_error_buffer();
+int fail(int code, const char* fmt, ...);
+
+#define CK_REQUIRE(cond, ...)                                            \
+  do {                                                                   \
+    if (!(cond)) return ::ck::fail(CK_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+#define CK_CUDA(call)                                                              \
+  do {                                                                             \
+    cudaError_t e__ = (call);                                                      \
+    if (e__ != cudaSuccess)                                                        \
+      return ::ck::fail(CK_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+__host__ __device__ constexpr int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+__host__ __device__ constexpr int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// ---- swizzled scale layout --------------------------------------------------
+// Byte offset of the scale of (row r, scale column c) in the 128x4-tiled
+// buffer: each tile of 128 rows x 4 columns is 512 contiguous bytes laid out
+// as 32 rows of 16 bytes; `col_tiles` = ceil(columns / 4).
+__host__ __device__ __forceinline__ int64_t swizzled_scale_offset(int64_t r, int64_t c, int64_t col_tiles) {
+  const int64_t tile = (r >> 7) * col_tiles + (c >> 2);
+  return tile * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
+}
+
+// ---- 256-bit global memory access (sm_100) ------------------------------------
+struct __align__(32) Vec256 {
+  uint32_t w[8];
+};
+
+__device__ __forceinline__ Vec256 ld_global_stream_256(const void* p) {
+  Vec256 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]), "=r"(r.w[5]),
+                 "=r"(r.w[6]), "=r"(r.w[7])
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ void st_global_256(void* p, const Vec256& r) {
+  asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.w[0]), "r"(r.w[1]),
+               "r"(r.w[2]), "r"(r.w[3]), "r"(r.w[4]), "r"(r.w[5]), "r"(r.w[6]), "r"(r.w[7])
+               : "memory");
+}
+
+}  // namespace ck

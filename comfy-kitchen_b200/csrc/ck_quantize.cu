@@ -1,0 +1,430 @@
+// Block quantizers for sm_100a: bf16/f16/f32 -> NVFP4 (E2M1 codes + E4M3 scales per
+// 16 elements) and -> MXFP8 (E4M3 data + E8M0 scales per 32 elements), both with the
+// scale bytes written straight into the 128x4-tiled layout the tensor cores consume.
+//
+// Both kernels are HBM-bound streaming kernels.  One thread owns one scale block of one
+// row, so a warp reads 32 consecutive blocks (1 KiB / 2 KiB of bf16) with 256-bit loads,
+// writes 256 B / 1 KiB of codes with 64-bit / 256-bit stores, and the four lanes that
+// share a 4-byte group of the scale tile merge their bytes by shuffle into one 32-bit
+// store.  The thread grid spans the *padded* scale tensor so that its padding bytes are
+// written as zero by the same launch (no separate memset).
+//
+// Arithmetic contract: results are bit-identical to the reference's eager path
+// (comfy_kitchen/backends/eager/quantization.py:115-160 and :257-324), which uses true
+// IEEE fp32 divisions.  This translation unit is therefore compiled without fast-math,
+// and every division below is either __fdiv_rn or a reciprocal-FMA sequence that is
+// proven to round identically (see div_markstein).
+#include "ck_common.cuh"
+
+#include <atomic>
+#include <cstdlib>
+#include <type_traits>
+
+namespace ck {
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------
+// small-float converts (hardware cvt; rounding = nearest-even, saturating)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t f32_to_e4m3_byte(float v) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(v));
+  return r & 0xFFu;
+}
+
+__device__ __forceinline__ float e4m3_byte_to_f32(uint32_t b) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(b)));
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xFFFFu)));
+}
+
+// byte = e2m1(hi) << 4 | e2m1(lo)
+__device__ __forceinline__ uint32_t f32x2_to_e2m1_byte(float hi, float lo) {
+  uint16_t r;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// 16-bit = e4m3(hi) << 8 | e4m3(lo)
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float hi, float lo) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// ---------------------------------------------------------------------------
+// a / b, correctly rounded, from y = RN(1/b) with five FMA-class operations.
+//
+// q0 = RN(a*y) is within 2 ulp of a/b; one residual correction makes q1 a faithful
+// quotient (error of q0 + r0*y against a/b is below 2^-46 relative), and by Markstein's
+// theorem a second correction from a faithful quotient with a correctly rounded
+// reciprocal yields RN(a/b), provided every residual is exact.  The caller guarantees
+// the exponent window in which that holds (see nvfp4_block) and falls back to
+// __fdiv_rn outside it.  The sign of `a` is re-applied at the end because an all-zero
+// FMA chain loses a negative zero.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float div_markstein(float a, float b, float y) {
+  float q = __fmul_rn(a, y);
+  float r = __fmaf_rn(-b, q, a);
+  q = __fmaf_rn(r, y, q);
+  r = __fmaf_rn(-b, q, a);
+  q = __fmaf_rn(r, y, q);
+  return copysignf(q, a);
+}
+
+// ---------------------------------------------------------------------------
+// loading N consecutive elements of one row as exact float values
+// ---------------------------------------------------------------------------
+template <typename T>
+struct SrcTraits;
+template <>
+struct SrcTraits<__nv_bfloat16> {
+  __device__ static float to_f32(const __nv_bfloat16& v) { return __bfloat162float(v); }
+};
+template <>
+struct SrcTraits<__half> {
+  __device__ static float to_f32(const __half& v) { return __half2float(v); }
+};
+template <>
+struct SrcTraits<float> {
+  __device__ static float to_f32(const float& v) { return v; }
+};
+
+// 16 consecutive elements starting at `p` (32-byte aligned for 2-byte types).
+template <typename T>
+__device__ __forceinline__ void load16_vec(const T* p, float (&v)[16]) {
+  if constexpr (sizeof(T) == 2) {
+    const Vec256 raw = ld_global_stream_256(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        v[2 * i] = __uint_as_float(raw.w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(raw.w[i] & 0xFFFF0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&raw.w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+      }
+    }
+  } else {
+    const Vec256 lo = ld_global_stream_256(p);
+    const Vec256 hi = ld_global_stream_256(p + 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = __uint_as_float(lo.w[i]);
+      v[8 + i] = __uint_as_float(hi.w[i]);
+    }
+  }
+}
+
+// Same, element by element with bounds checks (ragged or misaligned inputs).
+template <typename T>
+__device__ __forceinline__ void load16_guarded(const T* base, int64_t row, int64_t col0, int64_t rows, int64_t cols,
+                                               float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t c = col0 + i;
+    v[i] = (row < rows && c < cols) ? SrcTraits<T>::to_f32(base[row * cols + c]) : 0.0f;
+  }
+}
+
+__device__ __forceinline__ float amax16(const float (&v)[16]) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+// Merge the scale bytes of the 4 lanes that share one 4-byte group of the scale tile and
+// store them with one 32-bit store from the first of the four lanes.
+__device__ __forceinline__ void store_scale_quad(uint8_t* scales, int64_t row, int64_t sc, int64_t col_tiles,
+                                                 uint32_t byte) {
+  uint32_t w = byte | (__shfl_xor_sync(0xFFFFFFFFu, byte, 1) << 8);
+  w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2) << 16;
+  if ((sc & 3) == 0) {
+    *reinterpret_cast<uint32_t*>(scales + swizzled_scale_offset(row, sc, col_tiles)) = w;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4
+// ---------------------------------------------------------------------------
+// One 16-element block -> 8 code bytes (returned as two words) and one E4M3 scale byte.
+// Steps follow comfy_kitchen/backends/eager/quantization.py:137-158 one to one.
+template <bool kFastDiv>
+__device__ __forceinline__ void nvfp4_block(const float (&v)[16], float g, bool hi_first, uint32_t& lo_word,
+                                            uint32_t& hi_word, uint32_t& scale_byte) {
+  const float amax = amax16(v);
+  float s = __fdiv_rn(__fdiv_rn(amax, 6.0f), g);  // :139-140, two true divisions
+  s = fminf(s, 448.0f);                           // :141
+  scale_byte = f32_to_e4m3_byte(s);               // :142
+  const float total = __fmul_rn(g, e4m3_byte_to_f32(scale_byte));  // :143
+  const bool dead = (total == 0.0f);              // :146
+  const float safe = dead ? 1.0f : total;         // :147
+
+  float q[16];
+  // The reciprocal-FMA quotient is exact while no residual can underflow and no
+  // quotient can overflow: divisor within 2^+-60 and amax no more than 2^20 divisors.
+  // Elements so small that their residual would underflow (|x| < 2^-90) have a
+  // quotient below 2^-30 and encode as (signed) zero under either formula.
+  const bool window = kFastDiv && (safe >= 0x1p-60f) && (safe <= 0x1p60f) && (amax <= safe * 0x1p20f);
+  if (window) {
+    const float y = __frcp_rn(safe);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], safe);  // :149
+  }
+  if (dead) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = 0.0f;  // :150 (positive zero, sign dropped)
+  }
+  // :154-158 clamp to +-6, round to E2M1 (satfinite does the clamp), pack two per byte.
+  uint32_t b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    b[i] = hi_first ? f32x2_to_e2m1_byte(q[2 * i], q[2 * i + 1]) : f32x2_to_e2m1_byte(q[2 * i + 1], q[2 * i]);
+  }
+  lo_word = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+  hi_word = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+}
+
+// Thread t of the grid owns (row, scale column) = (t / sc_pad, t % sc_pad) of the padded
+// scale tensor [rows_pad, sc_pad]; sc_pad is a multiple of 4, so aligned lane quads share
+// a row and a 4-byte scale group.
+template <typename T, bool kVec, bool kFastDiv>
+__global__ void __launch_bounds__(kThreads)
+quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_scale, uint8_t* __restrict__ codes,
+                      uint8_t* __restrict__ scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
+                      int64_t num_cols, int64_t sc_pad, int64_t total_threads, int hi_first) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (t >= total_threads) return;  // total_threads is a multiple of 32: whole warps leave together
+  const int64_t row = t / sc_pad;
+  const int64_t sc = t - row * sc_pad;
+  const int64_t n_sc = num_cols >> 4;
+  uint32_t scale_byte = 0;
+  if (row < num_rows && sc < n_sc) {
+    float v[16];
+    if constexpr (kVec) {
+      load16_vec(x + row * orig_cols + sc * 16, v);
+    } else {
+      load16_guarded(x, row, sc * 16, orig_rows, orig_cols, v);
+    }
+    const float g = __ldg(global_scale);
+    uint32_t lo, hi;
+    nvfp4_block<kFastDiv>(v, g, hi_first != 0, lo, hi, scale_byte);
+    *reinterpret_cast<uint2*>(codes + row * (num_cols >> 1) + sc * 8) = make_uint2(lo, hi);
+  }
+  store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte);
+}
+
+// ---------------------------------------------------------------------------
+// MXFP8
+// ---------------------------------------------------------------------------
+// clamp(ceil(log2(r)) + 127, 0, 254) for r >= 2^-127, from the bits of r
+// (comfy_kitchen/backends/eager/quantization.py:295-300).  r = amax/448 with amax an
+// f16/bf16 number is either an exact power of two or far enough from one that the
+// reference's float32 log2 cannot round across an integer, so this integer form is
+// bit-identical for those input types.
+__device__ __forceinline__ uint32_t e8m0_ceil_exponent(float r) {
+  const uint32_t bits = __float_as_uint(r);
+  const uint32_t e = bits >> 23;  // r > 0
+  const uint32_t frac = bits & 0x7FFFFFu;
+  uint32_t biased;
+  if (e == 0) {
+    biased = frac > 0x400000u ? 1u : 0u;  // [2^-127, 2^-126): exactly 2^-127 -> 0
+  } else {
+    biased = e + (frac != 0u);
+  }
+  return min(biased, 254u);
+}
+
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kThreads)
+quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
+                      int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols, int64_t sc_pad,
+                      int64_t total_threads) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (t >= total_threads) return;
+  const int64_t row = t / sc_pad;
+  const int64_t sc = t - row * sc_pad;
+  const int64_t n_sc = num_cols >> 5;
+  uint32_t scale_byte = 0;
+  if (row < num_rows && sc < n_sc) {
+    float lo[16], hi[16];
+    if constexpr (kVec) {
+      load16_vec(x + row * orig_cols + sc * 32, lo);
+      load16_vec(x + row * orig_cols + sc * 32 + 16, hi);
+    } else {
+      load16_guarded(x, row, sc * 32, orig_rows, orig_cols, lo);
+      load16_guarded(x, row, sc * 32 + 16, orig_rows, orig_cols, hi);
+    }
+    const float amax = fmaxf(amax16(lo), amax16(hi));          // :292
+    const float need = fmaxf(__fdiv_rn(amax, 448.0f), 0x1p-127f);  // :294-295
+    const uint32_t e = e8m0_ceil_exponent(need);               // :298-302
+    const bool dead = (amax == 0.0f);                          // :306
+    // :303-310: divide by 2^(e-127).  For e in [1, 253] that is an exact multiplication by
+    // 2^(127-e); e == 254 needs the subnormal 2^-127; e == 0 decodes to a zero scale and
+    // the reference divides by zero (inputs below 448 * 2^-127, outside the pinned domain).
+    float inv;
+    if (e == 0) {
+      inv = __int_as_float(0x7F800000);
+    } else if (e == 254) {
+      inv = 0x1p-127f;
+    } else {
+      inv = __uint_as_float((254u - e) << 23);
+    }
+    if (dead) inv = 0.0f;  // :307,311 -> all zeros (positive)
+    Vec256 out;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // :314-315 clamp to +-448 and round to E4M3: satfinite performs the clamp
+      const uint32_t p0 = f32x2_to_e4m3x2(dead ? 0.0f : lo[4 * i + 1] * inv, dead ? 0.0f : lo[4 * i] * inv);
+      const uint32_t p1 = f32x2_to_e4m3x2(dead ? 0.0f : lo[4 * i + 3] * inv, dead ? 0.0f : lo[4 * i + 2] * inv);
+      out.w[i] = p0 | (p1 << 16);
+      const uint32_t p2 = f32x2_to_e4m3x2(dead ? 0.0f : hi[4 * i + 1] * inv, dead ? 0.0f : hi[4 * i] * inv);
+      const uint32_t p3 = f32x2_to_e4m3x2(dead ? 0.0f : hi[4 * i + 3] * inv, dead ? 0.0f : hi[4 * i + 2] * inv);
+      out.w[4 + i] = p2 | (p3 << 16);
+    }
+    st_global_256(data + row * num_cols + sc * 32, out);
+    scale_byte = dead ? 0u : e;  // :318
+  }
+  store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte);
+}
+
+std::atomic<int> g_exact_division{-1};  // -1: not set, follow CK_EXACT_DIV
+
+bool use_exact_division() {
+  const int v = g_exact_division.load(std::memory_order_relaxed);
+  if (v >= 0) return v != 0;
+  // CK_EXACT_DIV=1 forces __fdiv_rn for every element (validation of the fast quotient).
+  static const bool env = [] {
+    const char* e = getenv("CK_EXACT_DIV");
+    return e != nullptr && e[0] == '1';
+  }();
+  return env;
+}
+
+template <typename T>
+int launch_nvfp4(const void* input, const float* gs, void* codes, void* scales, int64_t orig_rows, int64_t orig_cols,
+                 int64_t num_rows, int64_t num_cols, int hi_first, cudaStream_t stream) {
+  const int64_t sc_pad = round_up(num_cols / 16, 4);
+  const int64_t total = round_up(num_rows, 128) * sc_pad;
+  const int64_t grid = ceil_div(total, kThreads);
+  CK_REQUIRE(grid <= 0x7FFFFFFF, "quantize_nvfp4: tensor too large (%lld blocks)", (long long)grid);
+  // vector path: every 16-element run is inside the input and 32-byte aligned
+  const bool vec = (orig_rows == num_rows) && (orig_cols == num_cols) &&
+                   (reinterpret_cast<uintptr_t>(input) % 32 == 0);
+  const T* x = static_cast<const T*>(input);
+  uint8_t* c = static_cast<uint8_t*>(codes);
+  uint8_t* s = static_cast<uint8_t*>(scales);
+  const bool exact = use_exact_division();
+#define CK_LAUNCH(VEC, FAST)                                                                          \
+  quantize_nvfp4_kernel<T, VEC, FAST><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(          \
+      x, gs, c, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, total, hi_first)
+  if (vec) {
+    if (exact) CK_LAUNCH(true, false); else CK_LAUNCH(true, true);
+  } else {
+    if (exact) CK_LAUNCH(false, false); else CK_LAUNCH(false, true);
+  }
+#undef CK_LAUNCH
+  CK_CUDA(cudaGetLastError());
+  return CK_OK;
+}
+
+template <typename T>
+int launch_mxfp8(const void* input, void* data, void* scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
+                 int64_t num_cols, cudaStream_t stream) {
+  const int64_t sc_pad = round_up(num_cols / 32, 4);
+  const int64_t total = round_up(num_rows, 128) * sc_pad;
+  const int64_t grid = ceil_div(total, kThreads);
+  CK_REQUIRE(grid <= 0x7FFFFFFF, "quantize_mxfp8: tensor too large (%lld blocks)", (long long)grid);
+  const bool vec = (orig_rows == num_rows) && (orig_cols == num_cols) &&
+                   (reinterpret_cast<uintptr_t>(input) % 32 == 0) && (reinterpret_cast<uintptr_t>(data) % 32 == 0);
+  const T* x = static_cast<const T*>(input);
+  uint8_t* d = static_cast<uint8_t*>(data);
+  uint8_t* s = static_cast<uint8_t*>(scales);
+  if (vec) {
+    quantize_mxfp8_kernel<T, true><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+        x, d, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, total);
+  } else {
+    CK_REQUIRE(reinterpret_cast<uintptr_t>(data) % 32 == 0, "quantize_mxfp8: output must be 32-byte aligned");
+    quantize_mxfp8_kernel<T, false><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+        x, d, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, total);
+  }
+  CK_CUDA(cudaGetLastError());
+  return CK_OK;
+}
+
+int check_quant_shapes(const char* op, int64_t block, const void* input, const void* out, const void* scales,
+                       int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols) {
+  CK_REQUIRE(input && out && scales, "%s: null pointer", op);
+  CK_REQUIRE(orig_rows > 0 && orig_cols > 0, "%s: empty input [%lld, %lld]", op, (long long)orig_rows,
+             (long long)orig_cols);
+  CK_REQUIRE(num_cols % block == 0, "%s: num_cols=%lld is not a multiple of %lld", op, (long long)num_cols,
+             (long long)block);
+  const bool same = (num_rows == orig_rows && num_cols == orig_cols);
+  const bool padded = (num_rows == round_up(orig_rows, block) && num_cols == round_up(orig_cols, block));
+  CK_REQUIRE(same || padded, "%s: output [%lld, %lld] is neither the input shape [%lld, %lld] nor its %lld-padding",
+             op, (long long)num_rows, (long long)num_cols, (long long)orig_rows, (long long)orig_cols,
+             (long long)block);
+  CK_REQUIRE(reinterpret_cast<uintptr_t>(scales) % 4 == 0, "%s: block_scales must be 4-byte aligned", op);
+  return CK_OK;
+}
+
+}  // namespace
+}  // namespace ck
+
+extern "C" int ck_debug_set_exact_division(int on) {
+  const bool before = ck::use_exact_division();
+  ck::g_exact_division.store(on != 0 ? 1 : 0, std::memory_order_relaxed);
+  return before ? 1 : 0;
+}
+
+extern "C" int ck_quantize_nvfp4(const void* input, int input_dtype, const float* global_scale, void* codes,
+                                 void* block_scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
+                                 int64_t num_cols, int hi_first, void* stream) {
+  using namespace ck;
+  if (int rc = check_quant_shapes("quantize_nvfp4", 16, input, codes, block_scales, orig_rows, orig_cols, num_rows,
+                                  num_cols))
+    return rc;
+  CK_REQUIRE(global_scale != nullptr, "quantize_nvfp4: null global_scale");
+  CK_REQUIRE(reinterpret_cast<uintptr_t>(codes) % 8 == 0, "quantize_nvfp4: codes must be 8-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (input_dtype) {
+    case CK_DTYPE_BF16:
+      return launch_nvfp4<__nv_bfloat16>(input, global_scale, codes, block_scales, orig_rows, orig_cols, num_rows,
+                                         num_cols, hi_first, s);
+    case CK_DTYPE_F16:
+      return launch_nvfp4<__half>(input, global_scale, codes, block_scales, orig_rows, orig_cols, num_rows, num_cols,
+                                  hi_first, s);
+    case CK_DTYPE_F32:
+      return launch_nvfp4<float>(input, global_scale, codes, block_scales, orig_rows, orig_cols, num_rows, num_cols,
+                                 hi_first, s);
+    default:
+      return fail(CK_ERR_INVALID_ARGUMENT, "quantize_nvfp4: unsupported input dtype code %d", input_dtype);
+  }
+}
+
+extern "C" int ck_quantize_mxfp8(const void* input, int input_dtype, void* data, void* block_scales,
+                                 int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols,
+                                 void* stream) {
+  using namespace ck;
+  if (int rc = check_quant_shapes("quantize_mxfp8", 32, input, data, block_scales, orig_rows, orig_cols, num_rows,
+                                  num_cols))
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (input_dtype) {
+    case CK_DTYPE_BF16:
+      return launch_mxfp8<__nv_bfloat16>(input, data, block_scales, orig_rows, orig_cols, num_rows, num_cols, s);
+    case CK_DTYPE_F16:
+      return launch_mxfp8<__half>(input, data, block_scales, orig_rows, orig_cols, num_rows, num_cols, s);
+    case CK_DTYPE_F32:
+      return launch_mxfp8<float>(input, data, block_scales, orig_rows, orig_cols, num_rows, num_cols, s);
+    default:
+      return fail(CK_ERR_INVALID_ARGUMENT, "quantize_mxfp8: unsupported input dtype code %d", input_dtype);
+  }
+}

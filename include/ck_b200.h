@@ -1,0 +1,142 @@
+/*
+ * C ABI of the B200 (sm_100a) quantized-linear backend.
+ *
+ * Every entry point is launch-only: it validates its arguments on the host,
+ * enqueues kernels on the caller's stream and returns.  It never allocates or
+ * frees device memory, never synchronises and never reads device data on the
+ * host, so all of them may be called during CUDA-graph capture.  All pointers
+ * are device pointers unless stated; all buffers are owned by the caller.
+ *
+ * Return value: CK_OK (0) or a CK_ERR_* code; ck_last_error() returns a
+ * thread-local description of the last failure on the calling thread.
+ *
+ * Each declaration names the interface of the reference project
+ * (kijai/comfy-kitchen, paths relative to its root) that it replaces.
+ */
+#ifndef CK_B200_H_
+#define CK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CK_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define CK_API __attribute__((visibility("default")))
+#else
+#define CK_API
+#endif
+
+/* status codes */
+#define CK_OK 0
+#define CK_ERR_INVALID_ARGUMENT 1 /* bad pointer, shape, alignment or dtype code */
+#define CK_ERR_UNSUPPORTED 2      /* valid request this build has no kernel for */
+#define CK_ERR_CUDA 3             /* a CUDA runtime / driver call failed */
+
+/* dtype codes, identical to the reference's
+ * (comfy_kitchen/backends/cuda/dtype_dispatch.cuh:36-42,
+ *  comfy_kitchen/backends/eager/quantization.py:31-39) */
+#define CK_DTYPE_F32 0
+#define CK_DTYPE_F16 1
+#define CK_DTYPE_BF16 2
+
+/* epilogue activations of the fused linear entry points */
+#define CK_ACT_NONE 0
+#define CK_ACT_GELU_TANH 1
+
+/* ABI version of the loaded library (compare with CK_ABI_VERSION). */
+CK_API int ck_abi_version(void);
+
+/* Thread-local message of the last error returned on this thread ("" if none). */
+CK_API const char* ck_last_error(void);
+
+/* 1 if `device` is a compute-capability 10.x GPU these kernels can run on,
+ * 0 if not, negative CK_ERR_* on a CUDA error.  Replaces the import-time
+ * availability probe of comfy_kitchen/backends/cuda/__init__.py:672-691. */
+CK_API int ck_device_supported(int device);
+
+/* Validation aid with no counterpart in the reference: on != 0 makes
+ * ck_quantize_nvfp4 use an IEEE division instruction sequence for every element
+ * instead of the reciprocal-FMA quotient (the two are bit-identical; tests prove
+ * it by comparing them).  Process-wide; returns the previous setting. */
+CK_API int ck_debug_set_exact_division(int on);
+
+/*
+ * NVFP4 quantization: [orig_rows, orig_cols] f32/f16/bf16 row-major contiguous
+ * input -> packed E2M1 codes uint8 [num_rows, num_cols/2] and E4M3 block
+ * scales (one per 16 elements of a row) in the 128x4-tiled "swizzled" layout,
+ * uint8 [roundup(num_rows,128), roundup(num_cols/16,4)], padding entries
+ * written as 0.  num_rows/num_cols are the output's logical dimensions: equal
+ * to orig_* or, with padding, orig_* rounded up to a multiple of 16 (the pad
+ * reads as zeros).  num_cols must be a multiple of 16.  global_scale points to
+ * one fp32 value in device memory.  hi_first != 0 puts the even-indexed
+ * element of each pair in the high nibble.
+ * Arithmetic is bit-identical to comfy_kitchen/backends/eager/quantization.py:115-160.
+ * Replaces launch_quantize_nvfp4_kernel,
+ * comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:323-335.
+ */
+CK_API int ck_quantize_nvfp4(const void* input, int input_dtype, const float* global_scale,
+                      void* codes, void* block_scales,
+                      int64_t orig_rows, int64_t orig_cols,
+                      int64_t num_rows, int64_t num_cols,
+                      int hi_first, void* stream);
+
+/*
+ * MXFP8 quantization: same input contract -> E4M3 data uint8 [num_rows,
+ * num_cols] and E8M0 block scales (one per 32 elements of a row) in the
+ * swizzled layout, uint8 [roundup(num_rows,128), roundup(num_cols/32,4)].
+ * num_cols must be a multiple of 32; num_rows/num_cols equal orig_* or orig_*
+ * rounded up to a multiple of 32.
+ * Arithmetic is bit-identical to comfy_kitchen/backends/eager/quantization.py:257-324
+ * for f16/bf16 inputs.
+ * Replaces launch_quantize_mxfp8_kernel,
+ * comfy_kitchen/backends/cuda/ops/quantize_mxfp8.cu:148-157.
+ */
+CK_API int ck_quantize_mxfp8(const void* input, int input_dtype,
+                      void* data, void* block_scales,
+                      int64_t orig_rows, int64_t orig_cols,
+                      int64_t num_rows, int64_t num_cols,
+                      void* stream);
+
+/*
+ * NVFP4 GEMM with linear semantics:
+ *   out[M,N] = cast( (deq(a)[M,K] . deq(b)[N,K]^T) * alpha + bias[N] )
+ * a: uint8 [M, K/2], b: uint8 [N, K/2] packed E2M1 (both operands with the same
+ * nibble order), sfa/sfb: E4M3 block scales in the swizzled layout with
+ * roundup(M|N,128) x roundup(K/16,4) bytes.  alpha = *alpha when alpha is
+ * non-null, else *tensor_scale_a * *tensor_scale_b (fp32, device memory).
+ * bias: null or [N] of bias_dtype (f16/bf16/f32).  out: [M,N] row-major of
+ * out_dtype (f32/f16/bf16).  K must be a multiple of 32, N a multiple of 8.
+ * fp32 accumulation in tensor memory (tcgen05 block-scaled MMA).
+ * Replaces launch_cublas_gemm_blockwise_fp4_kernel,
+ * comfy_kitchen/backends/cuda/ops/cublas_gemm_nvfp4.cu:297-311.
+ */
+CK_API int ck_scaled_mm_nvfp4(const void* a, const void* b, const void* sfa, const void* sfb,
+                       const float* tensor_scale_a, const float* tensor_scale_b,
+                       const float* alpha,
+                       const void* bias, int bias_dtype,
+                       void* out, int out_dtype,
+                       int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
+ * MXFP8 GEMM with linear semantics: out[M,N] = cast(deq(a) . deq(b)^T + bias).
+ * a: E4M3 bytes [M,K], b: E4M3 bytes [N,K], sfa/sfb: E8M0 block scales in the
+ * swizzled layout with roundup(M|N,128) x roundup(K/32,4) bytes.  K must be a
+ * multiple of 32, N a multiple of 8.
+ * Replaces the torch.nn.functional.scaled_mm call of
+ * comfy_kitchen/scaled_mm_v2.py:40-53 reached from
+ * comfy_kitchen/backends/eager/quantization.py:367-402 (the reference has no
+ * native kernel for this operator).
+ */
+CK_API int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa, const void* sfb,
+                       const void* bias, int bias_dtype,
+                       void* out, int out_dtype,
+                       int64_t M, int64_t N, int64_t K, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CK_B200_H_ */
