@@ -45,6 +45,7 @@ _SIGNATURES = {
     "ck_quantize_mxfp8": [_P, _I, _P, _P, _L, _L, _L, _L, _P],
     "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
+    "ck_gemm_status": [_P],
 }
 _RESTYPE = {"ck_last_error": ctypes.c_char_p}
 

@@ -136,6 +136,16 @@ CK_API int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa, con
                        void* out, int out_dtype,
                        int64_t M, int64_t N, int64_t K, void* stream);
 
+/*
+ * Device status word of the GEMM kernels.  Every wait inside them is bounded; a
+ * wait that gives up sets the word instead of hanging.  This call synchronises
+ * the current device, writes the word to *status_out (0 = all launches since the
+ * last call completed their waits) and clears it.  Host pointer.  Not for use
+ * during graph capture.  No counterpart in the reference (its GEMM is a cuBLASLt
+ * call, comfy_kitchen/backends/cuda/ops/cublas_gemm_nvfp4.cu:256-272).
+ */
+CK_API int ck_gemm_status(int* status_out);
+
 #ifdef __cplusplus
 }
 #endif

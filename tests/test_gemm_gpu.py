@@ -1,0 +1,193 @@
+"""GPU parity of the tcgen05 block-scaled GEMMs against eager-dequantize -> fp32 matmul.
+
+Tolerance (stated by the task): ||out - ref|| / ||ref|| <= 1e-3 for identical quantized
+operands, evaluated on float32 output; for bf16 / f16 output the reference is rounded to
+the output dtype first (rounding alone is ~1.7e-3 against an unrounded reference).
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+from conftest import golden_names, load_golden
+from gpu_util import as_f32, bits, dit_activation, dit_weight, layout_scale
+
+from oracle import ck_oracle as oc
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ck(cuda_device):
+    import comfy_kitchen
+
+    info = comfy_kitchen.list_backends()["cuda"]
+    assert info["available"], f"cuda backend not loaded: {info['unavailable_reason']}"
+    return comfy_kitchen
+
+
+def gemm_status() -> int:
+    import ctypes
+
+    from comfy_kitchen.backends import cuda as backend
+
+    v = ctypes.c_int(-1)
+    assert backend.load_library().ck_gemm_status(ctypes.byref(v)) == 0
+    return v.value
+
+
+def rel_err(out: np.ndarray, ref: np.ndarray) -> float:
+    return float(np.linalg.norm(out.astype(np.float64) - ref.astype(np.float64)) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30))
+
+
+def u8(a: np.ndarray, device, dtype=torch.uint8) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device).view(dtype)
+
+
+def bf16_from_bits(a: np.ndarray, device) -> torch.Tensor:
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(device)
+
+
+# ------------------------------------------------------------------------------------------ golden
+@pytest.mark.parametrize("name", golden_names("gemm_nvfp4_"))
+def test_nvfp4_golden(ck, cuda_device, name):
+    d = load_golden(name)
+    bias = bf16_from_bits(d["bias"], cuda_device) if "bias" in d else None
+    out = ck.scaled_mm_nvfp4(
+        u8(d["qa"], cuda_device), u8(d["qb"], cuda_device),
+        torch.tensor(float(d["sa"]), device=cuda_device), torch.tensor(float(d["sb"]), device=cuda_device),
+        u8(d["bsa"], cuda_device, torch.float8_e4m3fn), u8(d["bsb"], cuda_device, torch.float8_e4m3fn),
+        bias=bias, out_dtype=torch.float32)
+    assert gemm_status() == 0
+    assert rel_err(out.cpu().numpy(), d["ref"]) <= TOL
+
+
+@pytest.mark.parametrize("name", golden_names("gemm_mxfp8_"))
+def test_mxfp8_golden(ck, cuda_device, name):
+    d = load_golden(name)
+    bias = bf16_from_bits(d["bias"], cuda_device) if "bias" in d else None
+    out = ck.scaled_mm_mxfp8(
+        u8(d["qa"], cuda_device, torch.float8_e4m3fn), u8(d["qb"], cuda_device, torch.float8_e4m3fn),
+        u8(d["bsa"], cuda_device, torch.float8_e8m0fnu), u8(d["bsb"], cuda_device, torch.float8_e8m0fnu),
+        bias=bias, out_dtype=torch.float32)
+    assert gemm_status() == 0
+    assert rel_err(out.cpu().numpy(), d["ref"]) <= TOL
+
+
+# ------------------------------------------------------------------------------------------ oracle, seeded
+def _operands(m, n, k, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+    bias = (torch.randn(n, generator=g) * 0.01).bfloat16()
+    return a, b, bias
+
+
+def _check_nvfp4(ck, dev, a, b, bias, out_dtype):
+    sa, sb = layout_scale(a), layout_scale(b)
+    pad_a = a.shape[0] % 16 != 0
+    qa, bsa = ck.quantize_nvfp4(a.to(dev), sa.to(dev), pad_16x=pad_a)
+    qb, bsb = ck.quantize_nvfp4(b.to(dev), sb.to(dev))
+    out = ck.scaled_mm_nvfp4(qa, qb, sa.to(dev), sb.to(dev), bsa, bsb, bias=None if bias is None else bias.to(dev),
+                             out_dtype=out_dtype)
+    assert gemm_status() == 0
+    assert out.dtype == out_dtype and tuple(out.shape) == (qa.shape[0], b.shape[0])
+    ref = oc.scaled_mm_nvfp4(bits(qa), bits(qb), np.float32(sa.item()), np.float32(sb.item()), bits(bsa), bits(bsb),
+                             bias=None if bias is None else as_f32(bias))
+    got = out.float().cpu().numpy()
+    if out_dtype != torch.float32:
+        ref = torch.from_numpy(ref).to(out_dtype).float().numpy()
+    assert np.isfinite(got).all()
+    err = rel_err(got, ref)
+    assert err <= TOL, f"relative error {err:.3e}"
+    return err
+
+
+def _check_mxfp8(ck, dev, a, b, bias, out_dtype):
+    pad_a = a.shape[0] % 32 != 0
+    qa, bsa = ck.quantize_mxfp8(a.to(dev), pad_32x=pad_a)
+    qb, bsb = ck.quantize_mxfp8(b.to(dev))
+    out = ck.scaled_mm_mxfp8(qa, qb, bsa, bsb, bias=None if bias is None else bias.to(dev), out_dtype=out_dtype)
+    assert gemm_status() == 0
+    ref = oc.scaled_mm_mxfp8(bits(qa), bits(qb), bits(bsa), bits(bsb), bias=None if bias is None else as_f32(bias))
+    got = out.float().cpu().numpy()
+    if out_dtype != torch.float32:
+        ref = torch.from_numpy(ref).to(out_dtype).float().numpy()
+    assert np.isfinite(got).all()
+    err = rel_err(got, ref)
+    assert err <= TOL, f"relative error {err:.3e}"
+    return err
+
+
+SHAPES = [
+    # (M, N, K): single tile, K tails (K not a multiple of one pipeline stage), ragged M and N, many tiles
+    (128, 128, 256), (128, 256, 256), (128, 128, 64), (128, 128, 32), (128, 128, 288), (128, 128, 1024),
+    (16, 128, 256), (1, 8, 64), (48, 136, 192), (129, 264, 320), (256, 3072, 3072), (300, 520, 544),
+    (1024, 1024, 1024), (2048, 2560, 512),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_nvfp4_matches_oracle(ck, cuda_device, shape):
+    m, n, k = shape
+    a, b, bias = _operands(m, n, k, seed=m * 31 + n * 17 + k)
+    _check_nvfp4(ck, cuda_device, a, b, bias, torch.float32)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_mxfp8_matches_oracle(ck, cuda_device, shape):
+    m, n, k = shape
+    a, b, bias = _operands(m, n, k, seed=m * 13 + n * 7 + k)
+    _check_mxfp8(ck, cuda_device, a, b, bias, torch.float32)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_output_dtypes_and_bias(ck, cuda_device, out_dtype, with_bias):
+    a, b, bias = _operands(256, 384, 512, seed=5)
+    _check_nvfp4(ck, cuda_device, a, b, bias if with_bias else None, out_dtype)
+    _check_mxfp8(ck, cuda_device, a, b, bias if with_bias else None, out_dtype)
+
+
+def test_alpha_overrides_tensor_scales(ck, cuda_device):
+    a, b, _ = _operands(128, 128, 256, seed=9)
+    dev = cuda_device
+    sa, sb = layout_scale(a).to(dev), layout_scale(b).to(dev)
+    qa, bsa = ck.quantize_nvfp4(a.to(dev), sa)
+    qb, bsb = ck.quantize_nvfp4(b.to(dev), sb)
+    base = ck.scaled_mm_nvfp4(qa, qb, sa, sb, bsa, bsb, out_dtype=torch.float32)
+    doubled = ck.scaled_mm_nvfp4(qa, qb, sa, sb, bsa, bsb, out_dtype=torch.float32, alpha=(sa * sb * 2).reshape(1))
+    assert gemm_status() == 0
+    assert torch.equal(doubled, base * 2)
+
+
+# ------------------------------------------------------------------------------------------ full size
+def test_dit_projection_full_size(ck, cuda_device):
+    """x [4096,3072] with outliers, W [3072,3072], bias: both formats, bf16 output, against the oracle."""
+    a = dit_activation(4096, 3072)
+    b = dit_weight(3072, 3072)
+    g = torch.Generator(device="cpu").manual_seed(2)
+    bias = (torch.randn(3072, generator=g) * 0.01).bfloat16()
+    e4 = _check_nvfp4(ck, cuda_device, a, b, bias, torch.float32)
+    e8 = _check_mxfp8(ck, cuda_device, a, b, bias, torch.float32)
+    _check_nvfp4(ck, cuda_device, a, b, bias, torch.bfloat16)
+    _check_mxfp8(ck, cuda_device, a, b, bias, torch.bfloat16)
+    print(f"full-size relative error: nvfp4 {e4:.2e}, mxfp8 {e8:.2e}")
+
+
+def test_gemm_is_deterministic_and_row_independent(ck, cuda_device):
+    """Size-independent properties: repeat launches are bit-identical, and a row of the
+    output depends only on the same row of A (computing a slice gives the same bits)."""
+    dev = cuda_device
+    a, b, bias = _operands(1024, 768, 1024, seed=77)
+    sa, sb = layout_scale(a).to(dev), layout_scale(b).to(dev)
+    qa, bsa = ck.quantize_nvfp4(a.to(dev), sa)
+    qb, bsb = ck.quantize_nvfp4(b.to(dev), sb)
+    o1 = ck.scaled_mm_nvfp4(qa, qb, sa, sb, bsa, bsb, bias=bias.to(dev))
+    o2 = ck.scaled_mm_nvfp4(qa, qb, sa, sb, bsa, bsb, bias=bias.to(dev))
+    assert torch.equal(o1, o2)
+    qa_top, bsa_top = ck.quantize_nvfp4(a[:256].to(dev), sa)
+    o_top = ck.scaled_mm_nvfp4(qa_top, qb, sa, sb, bsa_top, bsb, bias=bias.to(dev))
+    assert gemm_status() == 0
+    assert torch.equal(o_top, o1[:256])
