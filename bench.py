@@ -1,0 +1,484 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--case CASE]
+
+One *step* is one NVFP4 linear of the single-DiT-projection workload
+(x bf16 [4096,3072] with 0.1 % x20 outliers, W bf16 [3072,3072] ~N(0,0.02)
+pre-quantized, bias bf16): ``quantize_nvfp4(x)`` followed by ``scaled_mm_nvfp4`` with
+bias into a bf16 [4096,3072] output.  ``value`` is 2*M*N*K / step time in TFLOP/s with
+the inputs resident in HBM; every step uses a different x / W / output buffer out of a
+ring whose total size exceeds the L2 cache.  With --gpus N (launched under torchrun) each
+rank runs the same step on its own data (the batch shards data-parallel, no collective
+on the data path), and the value is the aggregate over ranks.
+
+Other cases time one kernel alone (used for profiling and the per-kernel rooflines):
+quantize_nvfp4, quantize_mxfp8, gemm_nvfp4, gemm_mxfp8, linear_mxfp8.
+
+The JSON line also carries: ``e2e`` (the same step through the public Python API with
+host buffers: pinned-host x -> device, linear, bf16 result -> host), ``roofline`` for the
+dominant kernel (the GEMM), ``roofline_quantize``, ``cpu_baseline`` (the numpy oracle of
+the same path timed on the host), ``clocks`` sampled during the timed region, and
+``gpu_launches``.
+
+--impl reference times the CPU restatement of the reference's eager path (oracle/) on the
+host cores for the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "comfy-kitchen_b200"))
+sys.path.insert(0, ROOT)
+
+M, N, K = 4096, 3072, 3072
+WORKLOAD = "single DiT projection: x bf16 [4096,3072] ~N(0,1) + 0.1% x20 outliers, W bf16 [3072,3072] ~N(0,0.02), bias bf16; NVFP4 quantize(x) + scaled_mm + bias -> bf16"
+METRIC = "nvfp4_linear_tflops"
+NOMINAL_FP4_TFLOPS = 9000.0
+NOMINAL_FP8_TFLOPS = 4500.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------------------------
+# clocks sampling
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._proc = None
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        # one long-running nvidia-smi that prints a row every 50 ms
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                           "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                          stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        for raw in self._proc.stdout:
+            row = [c.strip() for c in raw.strip().split(",")]
+            if len(row) == 6:
+                self.samples.append(row)
+            if self._stop.is_set():
+                break
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        proc = getattr(self, "_proc", None)
+        if proc is not None:
+            proc.terminate()  # the exact child this object started
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(int(float(s[0])) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's eager path, timed on the host
+# --------------------------------------------------------------------------------------------
+def cpu_linear_once(rows: int, seed: int = 0) -> tuple[float, int]:
+    """One NVFP4 linear on `rows` rows of the workload through the numpy oracle. Returns (seconds, rows)."""
+    import numpy as np
+    import torch
+
+    from oracle import ck_oracle as oc
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn(rows, K, generator=g)
+    x = torch.where(torch.rand(rows, K, generator=g) < 0.001, x * 20, x).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.01).bfloat16().float().numpy()
+    sx = np.float32((x.abs().amax() / 2688.0).float().item())
+    sw = np.float32((w.abs().amax() / 2688.0).float().item())
+    xf, wf = x.float().numpy(), w.float().numpy()
+    qw, bsw = oc.quantize_nvfp4(wf, sw)  # weights are pre-quantized: not timed
+    t0 = time.perf_counter()
+    qx, bsx = oc.quantize_nvfp4(xf, sx)
+    out = oc.scaled_mm_nvfp4(qx, qw, sx, sw, bsx, bsw, bias=bias)
+    oc.f32_to_bf16_bits(out)
+    return time.perf_counter() - t0, rows
+
+
+def cpu_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args) -> dict:
+    """--impl reference: the CPU port of the reference's eager path, all host threads, bounded sample per step."""
+    import torch
+
+    torch.set_num_threads(cpu_threads())
+    rows = 1024  # bounded sample of the 4096-row workload per step
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_linear_once(rows)
+    times = []
+    for _ in range(args.steps):
+        dt, _ = cpu_linear_once(rows)
+        times.append(dt)
+    per_step = sum(times) / len(times)
+    tflops = 2.0 * rows * N * K / per_step / 1e12
+    sample = f"{rows} of {M} rows per step (quantize_nvfp4(x) + dequantize->fp32 matmul + bias -> bf16), numpy oracle, BLAS matmul"
+    return {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+class Workload:
+    """Device buffers of the step, as a ring of `ring` independent (x, W, out) sets."""
+
+    def __init__(self, torch, ck, device, rows: int, ring: int, seed: int):
+        self.torch, self.rows, self.ring, self.device = torch, rows, ring, device
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        x = torch.randn(rows, K, generator=g)
+        x = torch.where(torch.rand(rows, K, generator=g) < 0.001, x * 20, x).bfloat16()
+        w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+        self.bias = (torch.randn(N, generator=g) * 0.01).bfloat16().to(device)
+        self.x_host = x.pin_memory()
+        self.x = [x.to(device) if i == 0 else torch.roll(x, i, 0).to(device) for i in range(ring)]
+        self.sx = (x.abs().amax() / 2688.0).float().to(device).reshape(1)
+        self.sw = (w.abs().amax() / 2688.0).float().to(device).reshape(1)
+        wd = w.to(device)
+        self.w_bf16 = wd
+        # pre-quantized weights, `ring` copies so that successive steps do not share L2 lines
+        qw, bsw = ck.quantize_nvfp4(wd, self.sw)
+        self.qw = [qw.clone() for _ in range(ring)]
+        self.bsw = [bsw.view(torch.uint8).clone() for _ in range(ring)]
+        qw8, bsw8 = ck.quantize_mxfp8(wd)
+        self.qw8 = [qw8.view(torch.uint8).clone() for _ in range(ring)]
+        self.bsw8 = [bsw8.view(torch.uint8).clone() for _ in range(ring)]
+        u8 = dict(dtype=torch.uint8, device=device)
+        rp = (rows + 127) // 128 * 128
+        self.qx = [torch.empty(rows, K // 2, **u8) for _ in range(ring)]
+        self.bsx = [torch.empty(rp, K // 16, **u8) for _ in range(ring)]
+        self.qx8 = [torch.empty(rows, K, **u8) for _ in range(ring)]
+        self.bsx8 = [torch.empty(rp, K // 32, **u8) for _ in range(ring)]
+        self.out = [torch.empty(rows, N, dtype=torch.bfloat16, device=device) for _ in range(ring)]
+
+    def ring_bytes(self) -> int:
+        per = self.x[0].numel() * 2 + self.qw[0].numel() + self.bsw[0].numel() + self.out[0].numel() * 2 + \
+            self.qx[0].numel() + self.bsx[0].numel()
+        return per * self.ring
+
+
+def make_steps(lib, wl: Workload, case: str):
+    """Returns (launch(i, stream) -> None, kernels per step, flops per step, algorithmic bytes per step)."""
+    rows = wl.rows
+    p = lambda t: t.data_ptr()  # noqa: E731
+    flops = 2.0 * rows * N * K
+    q4_bytes = 2 * rows * K + rows * K // 2 + ((rows + 127) // 128 * 128) * (K // 16) + 4
+    q8_bytes = 2 * rows * K + rows * K + ((rows + 127) // 128 * 128) * (K // 32)
+
+    def q4(i, st):
+        j = i % wl.ring
+        rc = lib.ck_quantize_nvfp4(p(wl.x[j]), 2, p(wl.sx), p(wl.qx[j]), p(wl.bsx[j]), rows, K, rows, K, 1, st)
+        assert rc == 0, lib.ck_last_error()
+
+    def q8(i, st):
+        j = i % wl.ring
+        rc = lib.ck_quantize_mxfp8(p(wl.x[j]), 2, p(wl.qx8[j]), p(wl.bsx8[j]), rows, K, rows, K, st)
+        assert rc == 0, lib.ck_last_error()
+
+    def g4(i, st):
+        j = i % wl.ring
+        rc = lib.ck_scaled_mm_nvfp4(p(wl.qx[j]), p(wl.qw[j]), p(wl.bsx[j]), p(wl.bsw[j]), p(wl.sx), p(wl.sw), None,
+                                    p(wl.bias), 2, p(wl.out[j]), 2, rows, N, K, st)
+        assert rc == 0, lib.ck_last_error()
+
+    def g8(i, st):
+        j = i % wl.ring
+        rc = lib.ck_scaled_mm_mxfp8(p(wl.qx8[j]), p(wl.qw8[j]), p(wl.bsx8[j]), p(wl.bsw8[j]), p(wl.bias), 2,
+                                    p(wl.out[j]), 2, rows, N, K, st)
+        assert rc == 0, lib.ck_last_error()
+
+    table = {
+        "linear": (lambda i, st: (q4(i, st), g4(i, st)), 2, flops, None),
+        "linear_mxfp8": (lambda i, st: (q8(i, st), g8(i, st)), 2, flops, None),
+        "quantize_nvfp4": (q4, 1, None, q4_bytes),
+        "quantize_mxfp8": (q8, 1, None, q8_bytes),
+        "gemm_nvfp4": (g4, 1, flops, None),
+        "gemm_mxfp8": (g8, 1, flops, None),
+    }
+    return table[case]
+
+
+def time_steps(torch, launch, steps: int, warmup: int, use_graph: bool, dist=None) -> float:
+    """Device time in ms of `steps` launches after `warmup`, CUDA events on the launch stream.
+
+    With use_graph the steps are captured once into a CUDA graph (removes host launch
+    gaps between the short kernels) and the timed region is one replay."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        st = stream.cuda_stream
+        for i in range(warmup):
+            launch(i, st)
+        stream.synchronize()
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(steps):
+                    launch(warmup + i, st)
+            graph.replay()  # one untimed replay: graph upload
+            stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        if use_graph:
+            graph.replay()
+        else:
+            for i in range(steps):
+                launch(warmup + i, st)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        return e0.elapsed_time(e1)
+
+
+def run_e2e(torch, ck, wl: Workload, steps: int, warmup: int, dist=None) -> dict:
+    """The step through the public API with host buffers: H2D of x, linear, D2H of the bf16 result."""
+    dev = wl.device
+    qw, bsw = wl.qw[0], wl.bsw[0].view(torch.float8_e4m3fn)
+    out_host = torch.empty(wl.rows, N, dtype=torch.bfloat16).pin_memory()
+
+    def step():
+        x = wl.x_host.to(dev, non_blocking=True)
+        qx, bsx = ck.quantize_nvfp4(x, wl.sx)
+        y = ck.scaled_mm_nvfp4(qx, qw, wl.sx, wl.sw, bsx, bsw, bias=wl.bias, out_dtype=torch.bfloat16)
+        out_host.copy_(y, non_blocking=True)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    return {"ms": ms, "h2d": wl.x_host.numel() * 2, "d2h": out_host.numel() * 2}
+
+
+def run_gpu_arm(args) -> dict | None:
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # type: ignore[no-redef]
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the hot path has no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    device = torch.device(f"cuda:{local_rank}")
+
+    import comfy_kitchen as ck
+    from comfy_kitchen.backends import cuda as backend
+
+    info = ck.list_backends()["cuda"]
+    if not info["available"]:
+        raise SystemExit(f"cuda backend unavailable: {info['unavailable_reason']}")
+    lib = backend.load_library()
+    peaks, peak_kind = load_peaks()
+
+    rows = args.rows or M
+    ring = args.ring
+    wl = Workload(torch, ck, device, rows, ring, seed=rank)
+    launch, kernels_per_step, flops, alg_bytes = make_steps(lib, wl, args.case)
+    use_graph = not args.no_graph
+
+    with ClockSampler(local_rank) as clocks:
+        ms = time_steps(torch, launch, args.steps, args.warmup, use_graph, dist)
+        # per-kernel timings for the rooflines (same buffers, each kernel alone)
+        extra = {}
+        if args.case == "linear" and not args.skip_extras:
+            for name in ("gemm_nvfp4", "quantize_nvfp4", "gemm_mxfp8", "quantize_mxfp8"):
+                l2, _, fl2, by2 = make_steps(lib, wl, name)
+                extra[name] = (time_steps(torch, l2, args.steps, args.warmup, use_graph, dist) / args.steps, fl2, by2)
+        # keep the sampler running long enough to see the clocks under load
+        t_end = time.time() + 0.6
+        spin_stream = torch.cuda.Stream()
+        with torch.cuda.stream(spin_stream):
+            i = 0
+            while time.time() < t_end:
+                launch(i, spin_stream.cuda_stream)
+                i += 1
+                if i % 64 == 0:
+                    spin_stream.synchronize()
+            spin_stream.synchronize()
+    status = ctypes.c_int(0)
+    lib.ck_gemm_status(ctypes.byref(status))
+    if status.value != 0:
+        raise SystemExit("GEMM kernel reported a wait that gave up (device status word set); timing invalid")
+
+    e2e = None
+    if args.case == "linear" and not args.skip_extras:
+        e2e = run_e2e(torch, ck, wl, max(3, min(args.steps, 20)), 3, dist)
+        e2e["steps"] = max(3, min(args.steps, 20))
+
+    # max over ranks of the device time
+    if dist is not None:
+        t = torch.tensor([ms, e2e["ms"] / e2e["steps"] if e2e else 0.0], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0].item())
+        if e2e:
+            e2e["ms"] = float(t[1].item()) * e2e["steps"]
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return None
+
+    ms_per_step = ms / args.steps
+    line = {
+        "metric": METRIC if args.case == "linear" else args.case,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+        "config": {"workload": WORKLOAD if rows == M else f"{args.case} on {rows} rows of the DiT projection operands",
+                   "M": rows, "N": N, "K": K, "case": args.case, "per_rank": "one replica of the step per GPU (batch data-parallel)",
+                   "l2": f"ring of {ring} independent buffer sets, {wl.ring_bytes() / 1e6:.0f} MB in total (> 126 MB L2)",
+                   "cuda_graph": use_graph},
+        "clocks": clocks.summary(),
+        "gpu_launches": args.steps * kernels_per_step,
+    }
+    if flops is not None:
+        line["value"] = world * flops / (ms_per_step * 1e-3) / 1e12
+        line["unit"] = "TFLOP/s"
+        line["dtype"] = "mxfp8 (e4m3 x ue8m0, fp32 accumulate)" if "mxfp8" in args.case else "nvfp4 (e2m1 x ue4m3, fp32 accumulate)"
+    else:
+        line["value"] = world * alg_bytes / (ms_per_step * 1e-3) / 1e9
+        line["unit"] = "GB/s"
+        line["dtype"] = "bf16 -> " + ("e4m3 + ue8m0" if "mxfp8" in args.case else "e2m1 + ue4m3")
+
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+
+    def tensor_roofline(ms_launch, fl, peak, nominal, kernel):
+        ach = fl / (ms_launch * 1e-3) / 1e12
+        return {"kernel": kernel, "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "peak_basis": f"{'4' if nominal == NOMINAL_FP4_TFLOPS else '2'} x bf16_tflops of {peak_kind} peaks",
+                "frac_of_nominal": ach / nominal, "nominal_peak": nominal, "traffic": None, "us_per_launch": ms_launch * 1e3}
+
+    def hbm_roofline(ms_launch, by, kernel):
+        ach = by / (ms_launch * 1e-3) / 1e9
+        return {"kernel": kernel, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": ach / peaks["hbm_gbs"], "peak_basis": f"hbm_gbs of {peak_kind} peaks", "traffic": None,
+                "algorithmic_bytes": by, "us_per_launch": ms_launch * 1e3}
+
+    if args.case == "linear" and extra:
+        line["roofline"] = tensor_roofline(extra["gemm_nvfp4"][0], extra["gemm_nvfp4"][1], fp4_peak, NOMINAL_FP4_TFLOPS, "scaled_mm_nvfp4")
+        line["roofline_quantize"] = hbm_roofline(extra["quantize_nvfp4"][0], extra["quantize_nvfp4"][2], "quantize_nvfp4")
+        line["roofline_mxfp8"] = {
+            "gemm": tensor_roofline(extra["gemm_mxfp8"][0], extra["gemm_mxfp8"][1], fp8_peak, NOMINAL_FP8_TFLOPS, "scaled_mm_mxfp8"),
+            "quantize": hbm_roofline(extra["quantize_mxfp8"][0], extra["quantize_mxfp8"][2], "quantize_mxfp8"),
+        }
+    elif flops is not None and args.case.startswith("gemm"):
+        is8 = "mxfp8" in args.case
+        line["roofline"] = tensor_roofline(ms_per_step, flops, fp8_peak if is8 else fp4_peak,
+                                           NOMINAL_FP8_TFLOPS if is8 else NOMINAL_FP4_TFLOPS, args.case)
+    elif alg_bytes is not None:
+        line["roofline"] = hbm_roofline(ms_per_step, alg_bytes, args.case)
+
+    if e2e:
+        per = e2e["ms"] / e2e["steps"]
+        line["e2e"] = {"value": world * 2.0 * rows * N * K / (per * 1e-3) / 1e12, "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": per,
+                       "api": "comfy_kitchen.quantize_nvfp4 + comfy_kitchen.scaled_mm_nvfp4 (pinned host x in, bf16 result out)"}
+    if args.case == "linear" and not args.skip_extras and not args.no_cpu_baseline:
+        import torch as _t
+
+        _t.set_num_threads(cpu_threads())
+        sample_rows = 1024
+        cpu_linear_once(256)
+        dt, _ = cpu_linear_once(sample_rows)
+        line["cpu_baseline"] = {
+            "value": 2.0 * sample_rows * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
+            "sample": f"{sample_rows} of {M} rows, one step: numpy oracle quantize_nvfp4(x) + dequantize->fp32 BLAS matmul + bias",
+            "seconds": dt}
+    if dist is not None:
+        dist.destroy_process_group()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default="linear",
+                    choices=["linear", "linear_mxfp8", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8"])
+    ap.add_argument("--rows", type=int, default=0, help="override M (profiling of one kernel on a different size)")
+    ap.add_argument("--ring", type=int, default=8, help="independent buffer sets cycled through (L2 defeat)")
+    ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--skip-extras", action="store_true", help="only the timed case: no per-kernel, e2e or CPU legs")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        print(json.dumps(run_reference_arm(args)), flush=True)
+        return
+    line = run_gpu_arm(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()
