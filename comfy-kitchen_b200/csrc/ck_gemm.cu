@@ -24,6 +24,7 @@
 #include <cuda_fp16.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -53,7 +54,8 @@ struct Config {
   static constexpr int kSfaBytes = kSfTilesPerStage * 512;
   static constexpr int kSfbBytes = kSfbRowBlocks * kSfTilesPerStage * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes =
+      STAGES * kStageBytes + 2 * TILE_N * 4 /*bias*/ + 1024 /*alignment slack*/ + 256 /*barriers*/;
   // tensor memory columns
   static constexpr int kAccCols = TILE_N;
   static constexpr int kSfaCol = NUM_ACC * kAccCols;
@@ -88,48 +90,61 @@ struct GemmParams {
 
 __device__ int g_gemm_status = 0;
 
+// 32 consecutive output columns of one row: scale, add bias, convert, store.
+// `bias_s` points at the 32 fp32 bias values of these columns in shared memory (all lanes
+// read the same addresses: broadcast).  `vec_ok`: the row pitch and column offset allow
+// 32-byte aligned vector stores.
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[32], int valid) {
-  // dst points at 32 consecutive output columns of one row; `valid` of them exist.
-  if constexpr (sizeof(OutT) == 2) {
-    if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+__device__ __forceinline__ void finish_row_chunk(OutT* dst, const uint32_t (&raw)[32], float alpha,
+                                                 const float* bias_s, int valid, bool vec_ok) {
+  float v[32];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t w[4];
+  for (int i = 0; i < 8; ++i) {
+    const float4 b = reinterpret_cast<const float4*>(bias_s)[i];
+    v[4 * i + 0] = fmaf(__uint_as_float(raw[4 * i + 0]), alpha, b.x);
+    v[4 * i + 1] = fmaf(__uint_as_float(raw[4 * i + 1]), alpha, b.y);
+    v[4 * i + 2] = fmaf(__uint_as_float(raw[4 * i + 2]), alpha, b.z);
+    v[4 * i + 3] = fmaf(__uint_as_float(raw[4 * i + 3]), alpha, b.w);
+  }
+  if (valid == 32 && vec_ok) {
+    if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+      for (int h = 0; h < 2; ++h) {
+        Vec256 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
           if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
-            __nv_bfloat162 p = __floats2bfloat162_rn(v[i * 8 + 2 * j], v[i * 8 + 2 * j + 1]);
-            w[j] = *reinterpret_cast<uint32_t*>(&p);
+            __nv_bfloat162 q = __floats2bfloat162_rn(v[h * 16 + 2 * j], v[h * 16 + 2 * j + 1]);
+            o.w[j] = *reinterpret_cast<uint32_t*>(&q);
           } else {
-            __half2 p = __floats2half2_rn(v[i * 8 + 2 * j], v[i * 8 + 2 * j + 1]);
-            w[j] = *reinterpret_cast<uint32_t*>(&p);
+            __half2 q = __floats2half2_rn(v[h * 16 + 2 * j], v[h * 16 + 2 * j + 1]);
+            o.w[j] = *reinterpret_cast<uint32_t*>(&q);
           }
         }
-        reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        st_global_256(reinterpret_cast<uint8_t*>(dst) + h * 32, o);
       }
-      return;
-    }
+    } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      if (i < valid) {
-        if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
-          dst[i] = __float2bfloat16_rn(v[i]);
-        } else {
-          dst[i] = __float2half_rn(v[i]);
-        }
+      for (int h = 0; h < 4; ++h) {
+        Vec256 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.w[j] = __float_as_uint(v[h * 8 + j]);
+        st_global_256(reinterpret_cast<uint8_t*>(dst) + h * 32, o);
       }
     }
-  } else {
-    if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    return;
+  }
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-      return;
+  for (int i = 0; i < 32; ++i) {
+    if (i < valid) {
+      if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+        dst[i] = __float2bfloat16_rn(v[i]);
+      } else if constexpr (std::is_same<OutT, __half>::value) {
+        dst[i] = __float2half_rn(v[i]);
+      } else {
+        dst[i] = v[i];
+      }
     }
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < valid) dst[i] = v[i];
   }
 }
 
@@ -151,7 +166,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem_b = smem_a + STAGES * Cfg::kABytes;
   uint8_t* smem_sfa = smem_b + STAGES * Cfg::kBBytes;
   uint8_t* smem_sfb = smem_sfa + STAGES * Cfg::kSfaBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sfb + STAGES * Cfg::kSfbBytes);
+  float* smem_bias = reinterpret_cast<float*>(smem_sfb + STAGES * Cfg::kSfbBytes);  // [2][TILE_N]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bias + 2 * TILE_N);
   uint64_t* full_bar = bars;                       // [STAGES] producer -> MMA
   uint64_t* empty_bar = bars + STAGES;             // [STAGES] MMA -> producer
   uint64_t* acc_full_bar = bars + 2 * STAGES;      // [NUM_ACC] MMA -> epilogue
@@ -186,102 +202,117 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int k_stages = (p.k_bytes + kStageKBytes - 1) / kStageKBytes;
   const int total_mma = (p.k_bytes + kMmaKBytes - 1) / kMmaKBytes;
 
+  // The role loops below are executed by whole warps with warp-uniform control flow; the
+  // asynchronous instructions themselves are issued by one elected lane.
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        // consecutive CTAs work on tiles that share the B columns (tile_m fastest)
-        const int tile_m = tile % p.tiles_m;
-        const int tile_n = tile / p.tiles_m;
-        const int m0 = tile_m * kTileM;
-        const int n0 = tile_n * TILE_N;
-        const int rb_b0 = n0 / 128;
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      // consecutive CTAs work on tiles that share the B columns (tile_m fastest)
+      const int tile_m = tile % p.tiles_m;
+      const int tile_n = tile / p.tiles_m;
+      const int m0 = tile_m * kTileM;
+      const int n0 = tile_n * TILE_N;
+      const int rb_b0 = n0 / 128;
+      int rb_b_count = 0;
+#pragma unroll
+      for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) rb_b_count += (rb_b0 + r < p.n_row_blocks_b) ? 1 : 0;
+      const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(tile_m) * p.sf_col_tiles * 512;
+      const uint8_t* sfb_src = p.sfb + static_cast<int64_t>(rb_b0) * p.sf_col_tiles * 512;
+      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
+        if (elect_one()) {
           const int sf_tile0 = ks * Cfg::kSfTilesPerStage;
-          const int sf_tiles = min(Cfg::kSfTilesPerStage, p.sf_col_tiles - sf_tile0);
-          int rb_b_count = 0;
-          for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) rb_b_count += (rb_b0 + r < p.n_row_blocks_b) ? 1 : 0;
-          const uint32_t tx = Cfg::kABytes + Cfg::kBBytes + static_cast<uint32_t>(sf_tiles) * 512u * (1 + rb_b_count);
-          mbar_arrive_expect_tx(&full_bar[s], tx);
+          const uint32_t sf_bytes = static_cast<uint32_t>(min(Cfg::kSfTilesPerStage, p.sf_col_tiles - sf_tile0)) * 512u;
+          mbar_arrive_expect_tx(&full_bar[s], Cfg::kABytes + Cfg::kBBytes + sf_bytes * (1 + rb_b_count));
           tma_load_2d(smem_a + s * Cfg::kABytes, &map_a, &full_bar[s], ks * kStageKBytes, m0);
           tma_load_2d(smem_b + s * Cfg::kBBytes, &map_b, &full_bar[s], ks * kStageKBytes, n0);
-          bulk_load_1d(smem_sfa + s * Cfg::kSfaBytes,
-                       p.sfa + (static_cast<int64_t>(tile_m) * p.sf_col_tiles + sf_tile0) * 512, sf_tiles * 512,
-                       &full_bar[s]);
+          bulk_load_1d(smem_sfa + s * Cfg::kSfaBytes, sfa_src + sf_tile0 * 512, sf_bytes, &full_bar[s]);
+#pragma unroll
           for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
-            if (rb_b0 + r < p.n_row_blocks_b) {
+            if (r < rb_b_count) {
               bulk_load_1d(smem_sfb + s * Cfg::kSfbBytes + r * Cfg::kSfTilesPerStage * 512,
-                           p.sfb + (static_cast<int64_t>(rb_b0 + r) * p.sf_col_tiles + sf_tile0) * 512, sf_tiles * 512,
+                           sfb_src + (static_cast<int64_t>(r) * p.sf_col_tiles + sf_tile0) * 512, sf_bytes,
                            &full_bar[s]);
             }
           }
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t it = 0;
-      uint32_t tile_it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
-        const int tile_n = tile / p.tiles_m;
-        const int n0 = tile_n * TILE_N;
-        const int acc = tile_it % NUM_ACC;
-        const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
-        mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
+    // Descriptors differ between stages only in their start-address field, so the loop
+    // carries 32-bit low words; the high words are constants.
+    const uint32_t a_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_a)));
+    const uint32_t b_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_b)));
+    const uint32_t op_hi = static_cast<uint32_t>(make_operand_desc_sw128(0) >> 32);
+    const uint32_t sfa_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfa)));
+    const uint32_t sfb_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfb)));
+    const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
+    const uint32_t t_sfa = tmem_base + Cfg::kSfaCol;
+    const uint32_t t_sfb = tmem_base + Cfg::kSfbCol;
+    uint32_t it = 0;
+    uint32_t tile_it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
+      const int n0 = (tile / p.tiles_m) * TILE_N;
+      const int acc = tile_it % NUM_ACC;
+      const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
+      mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
+      // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
+      const uint32_t t_sfb_tile = t_sfb + (n0 % 128) / 32;
+      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        mbar_wait(&full_bar[s], ph, abort_flag);
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
-        // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
-        const uint32_t sfb_shift = (n0 % 128) / 32;
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          mbar_wait(&full_bar[s], ph, abort_flag);
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem_a + s * Cfg::kABytes);
-          const uint32_t b_addr = smem_u32(smem_b + s * Cfg::kBBytes);
-          const uint32_t sfa_addr = smem_u32(smem_sfa + s * Cfg::kSfaBytes);
-          const uint32_t sfb_addr = smem_u32(smem_sfb + s * Cfg::kSfbBytes);
-          // scale tiles of this stage: shared -> tensor memory
+        if (elect_one()) {
+          const uint32_t a_lo = a_lo0 + s * (Cfg::kABytes >> 4);
+          const uint32_t b_lo = b_lo0 + s * (Cfg::kBBytes >> 4);
+          const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
+          const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
+          const int n_mma = min(kMmaPerStage, total_mma - ks * kMmaPerStage);
+          // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units)
 #pragma unroll
           for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
-            tc_copy_scales_32x128b(tmem_base + Cfg::kSfaCol + t * 4, make_scale_desc(sfa_addr + t * 512));
+            tc_copy_scales_32x128b(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
 #pragma unroll
             for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
-              tc_copy_scales_32x128b(tmem_base + Cfg::kSfbCol + t * Cfg::kSfbColsPerTile + r * 4,
-                                     make_scale_desc(sfb_addr + (r * Cfg::kSfTilesPerStage + t) * 512));
+              tc_copy_scales_32x128b(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
+                                     desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
             }
           }
-          const uint64_t a_desc = make_operand_desc_sw128(a_addr);
-          const uint64_t b_desc = make_operand_desc_sw128(b_addr);
 #pragma unroll
           for (int kb = 0; kb < kMmaPerStage; ++kb) {
-            if (ks * kMmaPerStage + kb < total_mma) {
-              const uint32_t accumulate = (ks > 0 || kb > 0) ? 1u : 0u;
-              // advancing K inside the swizzle atom = advancing the start address
-              const uint64_t koff = static_cast<uint64_t>((kb * kMmaKBytes) >> 4);
+            if (kb < n_mma) {
+              const uint32_t accumulate = (ks | kb) != 0 ? 1u : 0u;
+              // advancing K inside the swizzle atom = advancing the start address (32 B = 2 units)
+              const uint64_t a_desc = desc64(a_lo + kb * 2, op_hi);
+              const uint64_t b_desc = desc64(b_lo + kb * 2, op_hi);
               if constexpr (KIND == Kind::kNvfp4) {
-                mma_nvfp4(d_tmem, a_desc + koff, b_desc + koff, Cfg::kIdesc, tmem_base + Cfg::kSfaCol + kb * 4,
-                          tmem_base + Cfg::kSfbCol + kb * Cfg::kSfbColsPerTile + sfb_shift, accumulate);
+                mma_nvfp4(d_tmem, a_desc, b_desc, Cfg::kIdesc, t_sfa + kb * 4, t_sfb_tile + kb * Cfg::kSfbColsPerTile,
+                          accumulate);
               } else {
-                // one scale tile serves the four MMAs of the stage; byte kb of each scale word
-                mma_mxfp8(d_tmem, a_desc + koff, b_desc + koff, idesc_with_scale_ids(Cfg::kIdesc, kb),
-                          tmem_base + Cfg::kSfaCol, tmem_base + Cfg::kSfbCol + sfb_shift, accumulate);
+                // one scale tile serves the four MMAs of the stage: byte kb of each scale word
+                mma_mxfp8(d_tmem, a_desc, b_desc, idesc_with_scale_ids(Cfg::kIdesc, kb), t_sfa, t_sfb_tile,
+                          accumulate);
               }
             }
           }
           tc_commit(&empty_bar[s]);  // stage reusable once these MMAs (and copies) retire
+          if (ks == k_stages - 1) tc_commit(&acc_full_bar[acc]);
         }
-        tc_commit(&acc_full_bar[acc]);
+        __syncwarp();
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // tensor-memory lanes this warp may read: 32*quarter .. +31
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
     float alpha = 1.0f;
     if (p.alpha != nullptr) {
       alpha = __ldg(p.alpha);
@@ -289,6 +320,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       alpha = __ldg(p.tsa) * __ldg(p.tsb);
     }
     OutT* out = static_cast<OutT*>(p.out);
+    const bool vec_ok = (static_cast<int64_t>(p.N) * sizeof(OutT)) % 32 == 0 &&
+                        (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (TILE_N * sizeof(OutT)) % 32 == 0;
     uint32_t tile_it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
       const int tile_m = tile % p.tiles_m;
@@ -297,32 +330,34 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int n0 = tile_n * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
+      // bias of this tile's columns as fp32 in shared memory (double-buffered across tiles)
+      float* bias_s = smem_bias + (tile_it & 1) * TILE_N;
+      for (int c = et; c < TILE_N; c += 128) {
+        const int n = n0 + c;
+        bias_s[c] = (p.bias != nullptr && n < p.N) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
       mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * Cfg::kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < TILE_N; c += 32) {
-        uint32_t raw[32];
-        tmem_load_32x32(t_row + c, raw);
+      OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0;
+      constexpr int kChunks = TILE_N / 32;
+      uint32_t buf[2][32];
+      tmem_load_32x32(t_row, buf[0]);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
         tmem_load_wait();
-        if (c + 32 >= TILE_N) {
-          // last read of this accumulator: hand it back before the stores
+        if (c + 1 < kChunks) {
+          tmem_load_32x32(t_row + (c + 1) * 32, buf[(c + 1) & 1]);
+        } else {
+          // every column of this accumulator is now in registers: hand it back
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
         }
-        const int col = n0 + c;
-        const int valid = min(32, p.N - col);
+        const int valid = min(32, p.N - (n0 + c * 32));
         if (row < p.M && valid > 0) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * alpha;
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] += load_bias(p.bias, p.bias_dtype, col + i);
-          }
-          store_row_chunk<OutT>(out + static_cast<int64_t>(row) * p.N + col, v, valid);
+          finish_row_chunk<OutT>(out_row + c * 32, buf[c & 1], alpha, bias_s + c * 32, valid, vec_ok);
         }
       }
     }
@@ -399,13 +434,34 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   return CK_OK;
 }
 
+int forced_tile_n() {
+  // CK_GEMM_TILE_N=128|192|256 pins the tile width (tuning aid); unset = choose by shape.
+  static const int v = [] {
+    const char* e = getenv("CK_GEMM_TILE_N");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
 template <Kind KIND, typename OutT>
-int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap& map_b128, const CUtensorMap& map_b256,
-                     const GemmParams& p, cudaStream_t stream) {
-  // Wide tiles when the problem fills the machine with them, else narrower tiles for more CTAs.
-  const int64_t tiles256 = ceil_div(p.M, kTileM) * ceil_div(p.N, 256);
-  if (tiles256 >= sm_count()) return launch_config<KIND, 256, 1, 4, OutT>(map_a, map_b256, p, stream);
-  return launch_config<KIND, 128, 2, 6, OutT>(map_a, map_b128, p, stream);
+int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[3], const GemmParams& p,
+                     cudaStream_t stream) {
+  // map_b[0|1|2] have boxes of 128 | 192 | 256 rows.
+  int tile_n = forced_tile_n();
+  if (tile_n == 0) {
+    // 192-wide tiles double-buffer the accumulator (epilogue overlaps the next main loop);
+    // narrower tiles only when the problem would otherwise leave SMs idle.
+    const int64_t tiles192 = ceil_div(p.M, kTileM) * ceil_div(p.N, 192);
+    tile_n = tiles192 >= sm_count() ? 192 : 128;
+  }
+  switch (tile_n) {
+    case 256:
+      return launch_config<KIND, 256, 1, 4, OutT>(map_a, map_b[2], p, stream);
+    case 192:
+      return launch_config<KIND, 192, 2, 4, OutT>(map_a, map_b[1], p, stream);
+    default:
+      return launch_config<KIND, 128, 2, 6, OutT>(map_a, map_b[0], p, stream);
+  }
 }
 
 template <Kind KIND>
@@ -446,18 +502,19 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
 
-  CUtensorMap map_a, map_b128, map_b256;
+  CUtensorMap map_a, map_b[3];
   if (int rc = make_operand_map(&map_a, a, M, p.k_bytes, kTileM)) return rc;
-  if (int rc = make_operand_map(&map_b128, b, N, p.k_bytes, 128)) return rc;
-  if (int rc = make_operand_map(&map_b256, b, N, p.k_bytes, 256)) return rc;
+  if (int rc = make_operand_map(&map_b[0], b, N, p.k_bytes, 128)) return rc;
+  if (int rc = make_operand_map(&map_b[1], b, N, p.k_bytes, 192)) return rc;
+  if (int rc = make_operand_map(&map_b[2], b, N, p.k_bytes, 256)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (out_dtype) {
     case CK_DTYPE_BF16:
-      return launch_for_shape<KIND, __nv_bfloat16>(map_a, map_b128, map_b256, p, s);
+      return launch_for_shape<KIND, __nv_bfloat16>(map_a, map_b, p, s);
     case CK_DTYPE_F16:
-      return launch_for_shape<KIND, __half>(map_a, map_b128, map_b256, p, s);
+      return launch_for_shape<KIND, __half>(map_a, map_b, p, s);
     default:
-      return launch_for_shape<KIND, float>(map_a, map_b128, map_b256, p, s);
+      return launch_for_shape<KIND, float>(map_a, map_b, p, s);
   }
 }
 
