@@ -12,8 +12,9 @@
 //             (tcgen05.cp), issues four tcgen05.mma per stage (32 bytes of K each) into a
 //             fp32 accumulator in tensor memory, and releases the stage / publishes the
 //             accumulator with tcgen05.commit.
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quarter),
-//             scale by alpha, add bias, convert, store; then hand the accumulator back.
+//   warps 2-9 epilogue: tcgen05.ld the accumulator into registers (two warps per 32-lane
+//             quarter, half the columns each), hand the accumulator back at once, then
+//             scale by alpha, add bias, convert and store while the next tile computes.
 // With NUM_ACC == 2 the epilogue of tile i overlaps the main loop of tile i+1.
 //
 // All synchronisation is by mbarriers with bounded waits (ck_sm100.cuh): a protocol error
@@ -39,17 +40,25 @@ constexpr int kTileM = 128;
 constexpr int kStageKBytes = 128;   // bytes of K per operand row per stage (one swizzle atom)
 constexpr int kMmaKBytes = 32;      // bytes of K per tcgen05.mma
 constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
-constexpr int kNumThreads = 192;    // 6 warps
+constexpr int kNumEpilogueWarps = 8;
+constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;  // TMA warp, MMA warp, epilogue warps
 constexpr int kTmemCols = 512;
 
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES>
+// CTAS == 2: a pair of CTAs (a 2-CTA cluster on neighbouring SMs) computes one 256 x TILE_N
+// tile with cta_group::2 instructions.  Each CTA loads its own 128 rows of A and only its
+// own half of B's rows, which halves the shared-memory traffic for B - the limiter of the
+// single-CTA FP4 kernel.
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS>
 struct Config {
+  static constexpr int kTileRows = kTileM * CTAS;      // rows of the output tile
+  static constexpr int kBRows = TILE_N / CTAS;         // rows of B each CTA loads
   static constexpr int kABytes = kTileM * kStageKBytes;
-  static constexpr int kBBytes = TILE_N * kStageKBytes;
+  static constexpr int kBBytes = kBRows * kStageKBytes;
   // 512-byte scale tiles (128 rows x 4 scale columns) one 128-row block needs per stage:
   // NVFP4 has 16 scale columns per 256 elements, MXFP8 4 per 128 elements.
   static constexpr int kSfTilesPerStage = (KIND == Kind::kNvfp4) ? 4 : 1;
-  // 128-row blocks of B's scale tensor a tile can touch (a 192-wide tile straddles two)
+  // 128-row blocks of B's scale tensor a tile can touch (a 192-wide tile straddles two);
+  // every CTA needs the scales of all TILE_N columns in its tensor memory.
   static constexpr int kSfbRowBlocks = (TILE_N + 127) / 128;
   static constexpr int kSfaBytes = kSfTilesPerStage * 512;
   static constexpr int kSfbBytes = kSfbRowBlocks * kSfTilesPerStage * 512;
@@ -63,11 +72,13 @@ struct Config {
   static constexpr int kSfbCol = kSfaCol + kSfaColsPerStage;
   static constexpr int kSfbColsPerTile = kSfbRowBlocks * 4;
   static constexpr int kSfbColsPerStage = kSfTilesPerStage * kSfbColsPerTile;
+  static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
+  static_assert(CTAS == 1 || TILE_N % 32 == 0, "a CTA pair needs N % 32 == 0");
   static_assert(kSfbCol + kSfbColsPerStage <= kTmemCols, "tensor memory budget exceeded");
   static_assert(TILE_N % 16 == 0 && TILE_N >= 16 && TILE_N <= 256, "invalid MMA N");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
   static constexpr uint32_t kIdesc = make_block_scaled_idesc(KIND == Kind::kNvfp4 ? 1u : 0u,
-                                                             KIND == Kind::kNvfp4 ? 0u : 1u, kTileM, TILE_N);
+                                                             KIND == Kind::kNvfp4 ? 0u : 1u, kTileRows, TILE_N);
 };
 
 struct GemmParams {
@@ -83,6 +94,7 @@ struct GemmParams {
   int M, N;
   int k_bytes;             // bytes of K per operand row
   int sf_col_tiles;        // 512-byte scale tiles per 128-row block = ceil(K / (4 * block))
+  int n_row_blocks_a;      // ceil(M / 128)
   int n_row_blocks_b;      // ceil(N / 128)
   int tiles_m, tiles_n;
   int* status;             // device status word: set non-zero when a wait gave up
@@ -154,11 +166,15 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
   return static_cast<const float*>(bias)[n];
 }
 
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, typename OutT>
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const GemmParams p) {
-  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES>;
+  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
+  // In a CTA pair, rank 0 (the leader) issues the MMAs for both CTAs.
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_cta_rank() : 0u;
+  const int worker = blockIdx.x / CTAS;        // index of this CTA (pair) among the tile workers
+  const int num_workers = gridDim.x / CTAS;
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -181,20 +197,22 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      // leader of a pair: its own producer plus the other CTA's "my stage is full" relay
+      mbar_init(&full_bar[s], (CTAS == 2 && cta_rank == 0) ? 2 : 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full_bar[a], 1);
-      mbar_init(&acc_empty_bar[a], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty_bar[a], kNumEpilogueWarps * CTAS);  // one arrival per epilogue warp (of both CTAs)
     }
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
   }
-  if (warp == 1) tmem_alloc(tmem_base_slot, kTmemCols);
+  if (warp == 1) tmem_alloc<CTAS>(tmem_base_slot, kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the other CTA's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
 
@@ -207,17 +225,19 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      // consecutive CTAs work on tiles that share the B columns (tile_m fastest)
+    for (int tile = worker; tile < num_tiles; tile += num_workers) {
+      // consecutive workers take tiles that share the B columns (tile_m fastest)
       const int tile_m = tile % p.tiles_m;
       const int tile_n = tile / p.tiles_m;
-      const int m0 = tile_m * kTileM;
+      const int m0 = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM;  // this CTA's rows of A
       const int n0 = tile_n * TILE_N;
       const int rb_b0 = n0 / 128;
       int rb_b_count = 0;
 #pragma unroll
       for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) rb_b_count += (rb_b0 + r < p.n_row_blocks_b) ? 1 : 0;
-      const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(tile_m) * p.sf_col_tiles * 512;
+      // the second CTA of a pair may own rows past M: it then has no scale row block to load
+      const bool have_sfa = (m0 / kTileM) < p.n_row_blocks_a;
+      const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(m0 / kTileM) * p.sf_col_tiles * 512;
       const uint8_t* sfb_src = p.sfb + static_cast<int64_t>(rb_b0) * p.sf_col_tiles * 512;
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
         const int s = it % STAGES;
@@ -226,10 +246,12 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (elect_one()) {
           const int sf_tile0 = ks * Cfg::kSfTilesPerStage;
           const uint32_t sf_bytes = static_cast<uint32_t>(min(Cfg::kSfTilesPerStage, p.sf_col_tiles - sf_tile0)) * 512u;
-          mbar_arrive_expect_tx(&full_bar[s], Cfg::kABytes + Cfg::kBBytes + sf_bytes * (1 + rb_b_count));
+          mbar_arrive_expect_tx(&full_bar[s],
+                                Cfg::kABytes + Cfg::kBBytes + sf_bytes * ((have_sfa ? 1 : 0) + rb_b_count));
           tma_load_2d(smem_a + s * Cfg::kABytes, &map_a, &full_bar[s], ks * kStageKBytes, m0);
-          tma_load_2d(smem_b + s * Cfg::kBBytes, &map_b, &full_bar[s], ks * kStageKBytes, n0);
-          bulk_load_1d(smem_sfa + s * Cfg::kSfaBytes, sfa_src + sf_tile0 * 512, sf_bytes, &full_bar[s]);
+          tma_load_2d(smem_b + s * Cfg::kBBytes, &map_b, &full_bar[s], ks * kStageKBytes,
+                      n0 + static_cast<int>(cta_rank) * Cfg::kBRows);
+          if (have_sfa) bulk_load_1d(smem_sfa + s * Cfg::kSfaBytes, sfa_src + sf_tile0 * 512, sf_bytes, &full_bar[s]);
 #pragma unroll
           for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
             if (r < rb_b_count) {
@@ -239,6 +261,19 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
           }
         }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1 && cta_rank != 0) {
+    // ------------------------------------------------------------------ relay (second CTA of a pair)
+    // Tells the leader when this CTA's copy of a stage has landed.
+    uint32_t it = 0;
+    for (int tile = worker; tile < num_tiles; tile += num_workers) {
+      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        mbar_wait(&full_bar[s], ph, abort_flag);
+        if (elect_one()) mbar_arrive_cluster(map_to_cta(smem_u32(&full_bar[s]), 0));
         __syncwarp();
       }
     }
@@ -254,13 +289,22 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
     const uint32_t t_sfa = tmem_base + Cfg::kSfaCol;
     const uint32_t t_sfb = tmem_base + Cfg::kSfbCol;
+    // barrier addresses: own, and (pair) the same barriers in the other CTA
+    const uint32_t empty_addr = smem_u32(empty_bar);
+    const uint32_t acc_full_addr = smem_u32(acc_full_bar);
+    const uint32_t empty_addr_peer = (CTAS == 2) ? map_to_cta(empty_addr, 1) : 0u;
+    const uint32_t acc_full_addr_peer = (CTAS == 2) ? map_to_cta(acc_full_addr, 1) : 0u;
     uint32_t it = 0;
     uint32_t tile_it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
+    for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
       const int n0 = (tile / p.tiles_m) * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
-      mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
+      if constexpr (CTAS == 2) {
+        mbar_wait_cluster(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
+      } else {
+        mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
+      }
       tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
       // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
@@ -268,7 +312,11 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        mbar_wait(&full_bar[s], ph, abort_flag);
+        if constexpr (CTAS == 2) {
+          mbar_wait_cluster(&full_bar[s], ph, abort_flag);
+        } else {
+          mbar_wait(&full_bar[s], ph, abort_flag);
+        }
         tc_fence_after_sync();
         if (elect_one()) {
           const uint32_t a_lo = a_lo0 + s * (Cfg::kABytes >> 4);
@@ -279,11 +327,11 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units)
 #pragma unroll
           for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
-            tc_copy_scales_32x128b(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
+            tc_copy_scales_32x128b<CTAS>(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
 #pragma unroll
             for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
-              tc_copy_scales_32x128b(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
-                                     desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
+              tc_copy_scales_32x128b<CTAS>(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
+                                           desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
             }
           }
 #pragma unroll
@@ -294,25 +342,38 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               const uint64_t a_desc = desc64(a_lo + kb * 2, op_hi);
               const uint64_t b_desc = desc64(b_lo + kb * 2, op_hi);
               if constexpr (KIND == Kind::kNvfp4) {
-                mma_nvfp4(d_tmem, a_desc, b_desc, Cfg::kIdesc, t_sfa + kb * 4, t_sfb_tile + kb * Cfg::kSfbColsPerTile,
-                          accumulate);
+                mma_nvfp4<CTAS>(d_tmem, a_desc, b_desc, Cfg::kIdesc, t_sfa + kb * 4,
+                                t_sfb_tile + kb * Cfg::kSfbColsPerTile, accumulate);
               } else {
                 // one scale tile serves the four MMAs of the stage: byte kb of each scale word
-                mma_mxfp8(d_tmem, a_desc, b_desc, idesc_with_scale_ids(Cfg::kIdesc, kb), t_sfa, t_sfb_tile,
-                          accumulate);
+                mma_mxfp8<CTAS>(d_tmem, a_desc, b_desc, idesc_with_scale_ids(Cfg::kIdesc, kb), t_sfa, t_sfb_tile,
+                                accumulate);
               }
             }
           }
-          tc_commit(&empty_bar[s]);  // stage reusable once these MMAs (and copies) retire
-          if (ks == k_stages - 1) tc_commit(&acc_full_bar[acc]);
+          // stage reusable (in both CTAs) once these MMAs and copies retire
+          tc_commit<CTAS>(empty_addr + s * 8);
+          if constexpr (CTAS == 2) tc_commit<CTAS>(empty_addr_peer + s * 8);
+          if (ks == k_stages - 1) {
+            tc_commit<CTAS>(acc_full_addr + acc * 8);
+            if constexpr (CTAS == 2) tc_commit<CTAS>(acc_full_addr_peer + acc * 8);
+          }
         }
         __syncwarp();
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each 32-lane quarter of tensor memory and split the tile's columns.
+    // A warp pulls its whole share of the accumulator into registers with back-to-back
+    // tcgen05.ld, hands the accumulator back to the MMA warp at once, and only then does
+    // the arithmetic and the stores - so the next tile's main loop overlaps them.
     const int quarter = warp & 3;  // tensor-memory lanes this warp may read: 32*quarter .. +31
-    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    const int half = (warp - 2) >> 2;
+    constexpr int kColsPerWarp = TILE_N / 2;
+    constexpr int kChunks = kColsPerWarp / 32;
+    static_assert(kColsPerWarp % 32 == 0, "tile width must split into 32-column chunks per warp");
+    const int et = threadIdx.x - 64;  // 0 .. 32*kNumEpilogueWarps-1 among the epilogue threads
     float alpha = 1.0f;
     if (p.alpha != nullptr) {
       alpha = __ldg(p.alpha);
@@ -322,42 +383,45 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_ok = (static_cast<int64_t>(p.N) * sizeof(OutT)) % 32 == 0 &&
                         (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (TILE_N * sizeof(OutT)) % 32 == 0;
+    const uint32_t acc_empty_leader = (CTAS == 2) ? map_to_cta(smem_u32(acc_empty_bar), 0) : 0u;
     uint32_t tile_it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
+    for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
       const int tile_m = tile % p.tiles_m;
       const int tile_n = tile / p.tiles_m;
-      const int row = tile_m * kTileM + quarter * 32 + lane;
+      const int row = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM + quarter * 32 + lane;
       const int n0 = tile_n * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
       // bias of this tile's columns as fp32 in shared memory (double-buffered across tiles)
       float* bias_s = smem_bias + (tile_it & 1) * TILE_N;
-      for (int c = et; c < TILE_N; c += 128) {
+      for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
         const int n = n0 + c;
         bias_s[c] = (p.bias != nullptr && n < p.N) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
       mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);
       tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + acc * Cfg::kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
-      OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0;
-      constexpr int kChunks = TILE_N / 32;
-      uint32_t buf[2][32];
-      tmem_load_32x32(t_row, buf[0]);
+      const int c0 = half * kColsPerWarp;
+      const uint32_t t_row = tmem_base + acc * Cfg::kAccCols + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
+      uint32_t buf[kChunks][32];
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) tmem_load_32x32(t_row + c * 32, buf[c]);
+      tmem_load_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CTAS == 2) {
+          mbar_arrive_cluster(acc_empty_leader + acc * 8);  // the leader's barrier counts both CTAs' warps
+        } else {
+          mbar_arrive(&acc_empty_bar[acc]);
+        }
+      }
+      OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0 + c0;
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
-        tmem_load_wait();
-        if (c + 1 < kChunks) {
-          tmem_load_32x32(t_row + (c + 1) * 32, buf[(c + 1) & 1]);
-        } else {
-          // every column of this accumulator is now in registers: hand it back
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
-        }
-        const int valid = min(32, p.N - (n0 + c * 32));
+        const int valid = min(32, p.N - (n0 + c0 + c * 32));
         if (row < p.M && valid > 0) {
-          finish_row_chunk<OutT>(out_row + c * 32, buf[c & 1], alpha, bias_s + c * 32, valid, vec_ok);
+          finish_row_chunk<OutT>(out_row + c * 32, buf[c], alpha, bias_s + c0 + c * 32, valid, vec_ok);
         }
       }
     }
@@ -372,9 +436,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (CTAS == 2) cluster_sync_all();  // no CTA leaves while its partner may still signal it
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<CTAS>(tmem_base, kTmemCols);
   }
 }
 
@@ -414,10 +479,10 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
   return CK_OK;
 }
 
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, typename OutT>
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT>
 int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, cudaStream_t stream) {
-  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES>;
-  auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, OutT>;
+  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
+  auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT>;
   // the dynamic shared-memory opt-in is per device: do it once for each device that launches
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -426,41 +491,58 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
     CK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
-  p.tiles_m = static_cast<int>(ceil_div(p.M, kTileM));
+  p.tiles_m = static_cast<int>(ceil_div(p.M, Cfg::kTileRows));
   p.tiles_n = static_cast<int>(ceil_div(p.N, TILE_N));
-  const int grid = min(p.tiles_m * p.tiles_n, sm_count());
-  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, p);
-  CK_CUDA(cudaGetLastError());
+  const int workers = min(p.tiles_m * p.tiles_n, sm_count() / CTAS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(workers * CTAS);
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p));
   return CK_OK;
 }
 
-int forced_tile_n() {
-  // CK_GEMM_TILE_N=128|192|256 pins the tile width (tuning aid); unset = choose by shape.
-  static const int v = [] {
-    const char* e = getenv("CK_GEMM_TILE_N");
-    return e ? atoi(e) : 0;
-  }();
-  return v;
+int forced_config() {
+  // CK_GEMM_CONFIG pins the kernel configuration (tuning aid); unset = choose by shape.
+  //   1 = one CTA, 128 x 128 tiles      2 = one CTA, 128 x 192 tiles (two accumulators)
+  //   3 = one CTA, 128 x 256 tiles      4 = CTA pair, 256 x 256 tiles
+  const char* e = getenv("CK_GEMM_CONFIG");
+  return e ? atoi(e) : 0;
 }
 
 template <Kind KIND, typename OutT>
 int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[3], const GemmParams& p,
                      cudaStream_t stream) {
   // map_b[0|1|2] have boxes of 128 | 192 | 256 rows.
-  int tile_n = forced_tile_n();
-  if (tile_n == 0) {
-    // 192-wide tiles double-buffer the accumulator (epilogue overlaps the next main loop);
-    // narrower tiles only when the problem would otherwise leave SMs idle.
-    const int64_t tiles192 = ceil_div(p.M, kTileM) * ceil_div(p.N, 192);
-    tile_n = tiles192 >= sm_count() ? 192 : 128;
+  int config = forced_config();
+  if (config == 0) {
+    const int64_t pair_tiles = ceil_div(p.M, 256) * ceil_div(p.N, 256);
+    const int64_t tiles256 = ceil_div(p.M, kTileM) * ceil_div(p.N, 256);
+    if (pair_tiles >= sm_count() / 2) {
+      config = 4;
+    } else if (tiles256 >= sm_count()) {
+      config = 3;
+    } else {
+      config = 1;
+    }
   }
-  switch (tile_n) {
-    case 256:
-      return launch_config<KIND, 256, 1, 4, OutT>(map_a, map_b[2], p, stream);
-    case 192:
-      return launch_config<KIND, 192, 2, 4, OutT>(map_a, map_b[1], p, stream);
+  switch (config) {
+    case 4:
+      return launch_config<KIND, 256, 1, 5, 2, OutT>(map_a, map_b[0], p, stream);
+    case 3:
+      return launch_config<KIND, 256, 1, 4, 1, OutT>(map_a, map_b[2], p, stream);
+    case 2:
+      return launch_config<KIND, 192, 2, 4, 1, OutT>(map_a, map_b[1], p, stream);
     default:
-      return launch_config<KIND, 128, 2, 6, OutT>(map_a, map_b[0], p, stream);
+      return launch_config<KIND, 128, 2, 6, 1, OutT>(map_a, map_b[0], p, stream);
   }
 }
 
@@ -499,6 +581,7 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.N = static_cast<int>(N);
   p.k_bytes = static_cast<int>(KIND == Kind::kNvfp4 ? K / 2 : K);
   p.sf_col_tiles = static_cast<int>(ceil_div(K / block, 4));
+  p.n_row_blocks_a = static_cast<int>(ceil_div(M, 128));
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
 
