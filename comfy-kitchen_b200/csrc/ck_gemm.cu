@@ -3,7 +3,8 @@
 //   NVFP4: A, B packed E2M1 (two per byte), E4M3 scale per 16 elements  (kind::mxf4nvf4)
 //   MXFP8: A, B E4M3 bytes,                  E8M0 scale per 32 elements  (kind::mxf8f6f4)
 //
-// One persistent CTA per SM, six warps with fixed roles:
+// One persistent CTA per SM (or, for large problems, one CTA pair per two SMs computing
+// 256 x 256 tiles with cta_group::2 instructions), ten warps with fixed roles:
 //   warp 0    TMA producer: per pipeline stage one 128-row x 128-byte box of A, one
 //             TILE_N-row box of B (128-byte swizzle) and the matching 512-byte scale tiles
 //             (linear bulk copies - in the tiled scale layout the tiles a stage needs are
@@ -69,12 +70,17 @@ struct Config {
   static constexpr int kAccCols = TILE_N;
   static constexpr int kSfaCol = NUM_ACC * kAccCols;
   static constexpr int kSfaColsPerStage = kSfTilesPerStage * 4;
-  static constexpr int kSfbCol = kSfaCol + kSfaColsPerStage;
+  static constexpr int kSfbCol = kSfaCol + kSfaColsPerStage;  // within one scale buffer
   static constexpr int kSfbColsPerTile = kSfbRowBlocks * 4;
   static constexpr int kSfbColsPerStage = kSfTilesPerStage * kSfbColsPerTile;
+  // The scale columns are multi-buffered like the shared-memory ring, so that the copies
+  // of the next stage do not have to wait for the MMAs still reading the previous ones.
+  static constexpr int kSfColsPerBuf = kSfaColsPerStage + kSfbColsPerStage;
+  static constexpr int kSfBufsFit = (kTmemCols - kSfaCol) / kSfColsPerBuf;
+  static constexpr int kSfBufs = kSfBufsFit < STAGES ? kSfBufsFit : STAGES;
+  static_assert(kSfBufs >= 1, "tensor memory budget exceeded");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
   static_assert(CTAS == 1 || TILE_N % 32 == 0, "a CTA pair needs N % 32 == 0");
-  static_assert(kSfbCol + kSfbColsPerStage <= kTmemCols, "tensor memory budget exceeded");
   static_assert(TILE_N % 16 == 0 && TILE_N >= 16 && TILE_N <= 256, "invalid MMA N");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
   static constexpr uint32_t kIdesc = make_block_scaled_idesc(KIND == Kind::kNvfp4 ? 1u : 0u,
@@ -169,6 +175,7 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
 template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                          const GemmParams p) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
   // In a CTA pair, rank 0 (the leader) issues the MMAs for both CTAs.
@@ -197,8 +204,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
-      // leader of a pair: its own producer plus the other CTA's "my stage is full" relay
-      mbar_init(&full_bar[s], (CTAS == 2 && cta_rank == 0) ? 2 : 1);
+      mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < NUM_ACC; ++a) {
@@ -242,7 +248,31 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
+        if constexpr (CTAS == 2) {
+          mbar_wait_cluster(&empty_bar[s], ph ^ 1, abort_flag);  // signalled from the leader CTA
+        } else {
+          mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
+        }
+        if constexpr (CTAS == 2) {
+          // Every load of both CTAs reports its bytes to the leader's barrier; scale tiles
+          // come through 3-D tensor maps {512 B, column tile, row block} so that tiles past
+          // the end read as zeros and every stage has the same byte count.
+          if (elect_one()) {
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * Cfg::kStageBytes);
+            const int sf_tile0 = ks * Cfg::kSfTilesPerStage;
+            tma_load_2d_pair(smem_a + s * Cfg::kABytes, &map_a, &full_bar[s], ks * kStageKBytes, m0);
+            tma_load_2d_pair(smem_b + s * Cfg::kBBytes, &map_b, &full_bar[s], ks * kStageKBytes,
+                             n0 + static_cast<int>(cta_rank) * Cfg::kBRows);
+            tma_load_3d_pair(smem_sfa + s * Cfg::kSfaBytes, &map_sfa, &full_bar[s], 0, sf_tile0, m0 / kTileM);
+#pragma unroll
+            for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
+              tma_load_3d_pair(smem_sfb + s * Cfg::kSfbBytes + r * Cfg::kSfTilesPerStage * 512, &map_sfb, &full_bar[s],
+                               0, sf_tile0, rb_b0 + r);
+            }
+          }
+          __syncwarp();
+          continue;
+        }
         if (elect_one()) {
           const int sf_tile0 = ks * Cfg::kSfTilesPerStage;
           const uint32_t sf_bytes = static_cast<uint32_t>(min(Cfg::kSfTilesPerStage, p.sf_col_tiles - sf_tile0)) * 512u;
@@ -265,18 +295,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else if (warp == 1 && cta_rank != 0) {
-    // ------------------------------------------------------------------ relay (second CTA of a pair)
-    // Tells the leader when this CTA's copy of a stage has landed.
-    uint32_t it = 0;
-    for (int tile = worker; tile < num_tiles; tile += num_workers) {
-      for (int ks = 0; ks < k_stages; ++ks, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        mbar_wait(&full_bar[s], ph, abort_flag);
-        if (elect_one()) mbar_arrive_cluster(map_to_cta(smem_u32(&full_bar[s]), 0));
-        __syncwarp();
-      }
-    }
+    // second CTA of a pair: the leader issues the MMAs for both
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // Descriptors differ between stages only in their start-address field, so the loop
@@ -287,9 +306,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t sfa_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfa)));
     const uint32_t sfb_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfb)));
     const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
-    const uint32_t t_sfa = tmem_base + Cfg::kSfaCol;
-    const uint32_t t_sfb = tmem_base + Cfg::kSfbCol;
-    // barrier addresses: own, and (pair) the same barriers in the other CTA
+    const uint32_t t_sfa0 = tmem_base + Cfg::kSfaCol;
+    const uint32_t t_sfb0 = tmem_base + Cfg::kSfbCol;
     const uint32_t empty_addr = smem_u32(empty_bar);
     const uint32_t acc_full_addr = smem_u32(acc_full_bar);
     const uint32_t empty_addr_peer = (CTAS == 2) ? map_to_cta(empty_addr, 1) : 0u;
@@ -308,7 +326,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
       // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
-      const uint32_t t_sfb_tile = t_sfb + (n0 % 128) / 32;
+      const uint32_t sfb_shift = (n0 % 128) / 32;
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -324,6 +342,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
           const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
           const int n_mma = min(kMmaPerStage, total_mma - ks * kMmaPerStage);
+          const uint32_t sf_buf = (it % Cfg::kSfBufs) * Cfg::kSfColsPerBuf;
+          const uint32_t t_sfa = t_sfa0 + sf_buf;
+          const uint32_t t_sfb = t_sfb0 + sf_buf;
+          const uint32_t t_sfb_tile = t_sfb + sfb_shift;
           // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units)
 #pragma unroll
           for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
@@ -351,7 +373,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               }
             }
           }
-          // stage reusable (in both CTAs) once these MMAs and copies retire
+          // stage reusable once these MMAs and copies retire; in a pair both CTAs are told
           tc_commit<CTAS>(empty_addr + s * 8);
           if constexpr (CTAS == 2) tc_commit<CTAS>(empty_addr_peer + s * 8);
           if (ks == k_stages - 1) {
@@ -399,7 +421,11 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         bias_s[c] = (p.bias != nullptr && n < p.N) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
-      mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);
+      if constexpr (CTAS == 2) {
+        mbar_wait_cluster(&acc_full_bar[acc], acc_ph, abort_flag);
+      } else {
+        mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);
+      }
       tc_fence_after_sync();
       const int c0 = half * kColsPerWarp;
       const uint32_t t_row = tmem_base + acc * Cfg::kAccCols + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
@@ -479,6 +505,22 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
   return CK_OK;
 }
 
+// Scale tensor in the tiled layout as a 3-D array {128 x uint32 (one 512-byte tile), column
+// tile, row block}; a box is `tiles` consecutive column tiles of one row block.
+int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64_t col_tiles, int tiles) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(col_tiles), static_cast<cuuint64_t>(row_blocks)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(col_tiles) * 512};
+  const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(tiles), 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with code %d", static_cast<int>(r));
+  return CK_OK;
+}
+
 template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT>
 int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, cudaStream_t stream) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
@@ -493,9 +535,7 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   }
   p.tiles_m = static_cast<int>(ceil_div(p.M, Cfg::kTileRows));
   p.tiles_n = static_cast<int>(ceil_div(p.N, TILE_N));
-  const int workers = min(p.tiles_m * p.tiles_n, sm_count() / CTAS);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(workers * CTAS);
   cfg.blockDim = dim3(kNumThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
@@ -506,7 +546,28 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p));
+  // Persistent workers must all be resident at once.  For CTA pairs the number of
+  // co-resident clusters can be below sm_count / 2 (pairs must sit in one GPC): ask.
+  static std::atomic<int> max_workers[64];
+  int resident = (dev >= 0 && dev < 64) ? max_workers[dev].load(std::memory_order_acquire) : 0;
+  if (resident == 0) {
+    resident = sm_count() / CTAS;
+    if (CTAS > 1) {
+      cfg.gridDim = dim3(sm_count() / CTAS * CTAS);
+      int clusters = 0;
+      CK_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+      if (clusters > 0) resident = min(resident, clusters);
+    }
+    if (dev >= 0 && dev < 64) max_workers[dev].store(resident, std::memory_order_release);
+  }
+  const int workers = min(p.tiles_m * p.tiles_n, resident);
+  cfg.gridDim = dim3(workers * CTAS);
+  CUtensorMap map_sfa = {}, map_sfb = {};
+  if (CTAS == 2) {
+    if (int rc = make_scale_map(&map_sfa, p.sfa, p.n_row_blocks_a, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
+    if (int rc = make_scale_map(&map_sfb, p.sfb, p.n_row_blocks_b, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
+  }
+  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, p));
   return CK_OK;
 }
 
@@ -617,6 +678,28 @@ extern "C" int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa,
                                   void* stream) {
   return ck::scaled_mm<ck::Kind::kMxfp8>("scaled_mm_mxfp8", a, b, sfa, sfb, nullptr, nullptr, nullptr, bias, bias_dtype,
                                          out, out_dtype, M, N, K, stream);
+}
+
+// Number of CTA pairs the 256x256 configuration runs concurrently on the current device
+// (diagnostic; 0 until that configuration has launched once).
+extern "C" int ck_debug_resident_pairs(void) {
+  cudaLaunchConfig_t cfg = {};
+  using Cfg = ck::Config<ck::Kind::kNvfp4, 256, 1, 5, 2>;
+  auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -1;
+  cfg.gridDim = dim3(ck::sm_count() / 2 * 2);
+  cfg.blockDim = dim3(ck::kNumThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) return -1;
+  return clusters;
 }
 
 // Device status word of the GEMM kernels: 0 = every wait completed; non-zero = some wait

@@ -136,6 +136,11 @@ CK_API int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa, con
                        void* out, int out_dtype,
                        int64_t M, int64_t N, int64_t K, void* stream);
 
+/* Diagnostic with no counterpart in the reference: how many 2-CTA clusters of the
+ * 256x256 GEMM configuration can be resident at once on the current device
+ * (negative on error). */
+CK_API int ck_debug_resident_pairs(void);
+
 /*
  * Device status word of the GEMM kernels.  Every wait inside them is bounded; a
  * wait that gives up sets the word instead of hanging.  This call synchronises
