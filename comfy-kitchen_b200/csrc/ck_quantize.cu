@@ -2,8 +2,9 @@
 // 16 elements) and -> MXFP8 (E4M3 data + E8M0 scales per 32 elements), both with the
 // scale bytes written straight into the 128x4-tiled layout the tensor cores consume.
 //
-// Both kernels are HBM-bound streaming kernels.  One thread owns one scale block of one
-// row, so a warp reads 32 consecutive blocks (1 KiB / 2 KiB of bf16) with 256-bit loads,
+// Both kernels are streaming kernels whose floor is HBM bandwidth.  One thread owns one scale
+// block of one row (2-D block and grid indices, no integer division), so a warp reads 32
+// consecutive blocks (1 KiB / 2 KiB of bf16) with 256-bit loads,
 // writes 256 B / 1 KiB of codes with 64-bit / 256-bit stores, and the four lanes that
 // share a 4-byte group of the scale tile merge their bytes by shuffle into one 32-bit
 // store.  The thread grid spans the *padded* scale tensor so that its padding bytes are
@@ -23,7 +24,9 @@
 namespace ck {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kColsPerBlock = 64;  // scale columns per thread block (two warps wide)
+constexpr int kRowsPerBlock = 4;
+constexpr int kThreads = kColsPerBlock * kRowsPerBlock;
 
 // ---------------------------------------------------------------------------
 // small-float converts (hardware cvt; rounding = nearest-even, saturating)
@@ -139,11 +142,12 @@ __device__ __forceinline__ float amax16(const float (&v)[16]) {
 
 // Merge the scale bytes of the 4 lanes that share one 4-byte group of the scale tile and
 // store them with one 32-bit store from the first of the four lanes.
+// Executed by every lane of the warp; lanes past the padded width (`inside` false) do not store.
 __device__ __forceinline__ void store_scale_quad(uint8_t* scales, int64_t row, int64_t sc, int64_t col_tiles,
-                                                 uint32_t byte) {
+                                                 uint32_t byte, bool inside) {
   uint32_t w = byte | (__shfl_xor_sync(0xFFFFFFFFu, byte, 1) << 8);
   w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2) << 16;
-  if ((sc & 3) == 0) {
+  if (inside && (sc & 3) == 0) {
     *reinterpret_cast<uint32_t*>(scales + swizzled_scale_offset(row, sc, col_tiles)) = w;
   }
 }
@@ -192,18 +196,17 @@ __device__ __forceinline__ void nvfp4_block(const float (&v)[16], float g, bool 
   hi_word = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
 }
 
-// Thread t of the grid owns (row, scale column) = (t / sc_pad, t % sc_pad) of the padded
-// scale tensor [rows_pad, sc_pad]; sc_pad is a multiple of 4, so aligned lane quads share
-// a row and a 4-byte scale group.
+// A thread owns one (row, scale column) of the padded scale tensor [rows_pad, sc_pad]:
+// block = (kColsPerBlock scale columns, kRowsPerBlock rows), grid = (row groups, column
+// chunks).  sc_pad is a multiple of 4 and a warp is 32 consecutive scale columns of one
+// row, so aligned lane quads share a row and a 4-byte scale group.
 template <typename T, bool kVec, bool kFastDiv>
 __global__ void __launch_bounds__(kThreads)
 quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_scale, uint8_t* __restrict__ codes,
                       uint8_t* __restrict__ scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
-                      int64_t num_cols, int64_t sc_pad, int64_t total_threads, int hi_first) {
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (t >= total_threads) return;  // total_threads is a multiple of 32: whole warps leave together
-  const int64_t row = t / sc_pad;
-  const int64_t sc = t - row * sc_pad;
+                      int64_t num_cols, int64_t sc_pad, int hi_first) {
+  const int64_t sc = blockIdx.y * kColsPerBlock + threadIdx.x;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + threadIdx.y;
   const int64_t n_sc = num_cols >> 4;
   uint32_t scale_byte = 0;
   if (row < num_rows && sc < n_sc) {
@@ -218,7 +221,7 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
     nvfp4_block<kFastDiv>(v, g, hi_first != 0, lo, hi, scale_byte);
     *reinterpret_cast<uint2*>(codes + row * (num_cols >> 1) + sc * 8) = make_uint2(lo, hi);
   }
-  store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte);
+  store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte, sc < sc_pad);
 }
 
 // ---------------------------------------------------------------------------
@@ -245,12 +248,9 @@ __device__ __forceinline__ uint32_t e8m0_ceil_exponent(float r) {
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads)
 quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
-                      int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols, int64_t sc_pad,
-                      int64_t total_threads) {
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (t >= total_threads) return;
-  const int64_t row = t / sc_pad;
-  const int64_t sc = t - row * sc_pad;
+                      int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols, int64_t sc_pad) {
+  const int64_t sc = blockIdx.y * kColsPerBlock + threadIdx.x;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + threadIdx.y;
   const int64_t n_sc = num_cols >> 5;
   uint32_t scale_byte = 0;
   if (row < num_rows && sc < n_sc) {
@@ -292,7 +292,7 @@ quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ data, uint8
     st_global_256(data + row * num_cols + sc * 32, out);
     scale_byte = dead ? 0u : e;  // :318
   }
-  store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte);
+  store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte, sc < sc_pad);
 }
 
 std::atomic<int> g_exact_division{-1};  // -1: not set, follow CK_EXACT_DIV
@@ -312,9 +312,10 @@ template <typename T>
 int launch_nvfp4(const void* input, const float* gs, void* codes, void* scales, int64_t orig_rows, int64_t orig_cols,
                  int64_t num_rows, int64_t num_cols, int hi_first, cudaStream_t stream) {
   const int64_t sc_pad = round_up(num_cols / 16, 4);
-  const int64_t total = round_up(num_rows, 128) * sc_pad;
-  const int64_t grid = ceil_div(total, kThreads);
-  CK_REQUIRE(grid <= 0x7FFFFFFF, "quantize_nvfp4: tensor too large (%lld blocks)", (long long)grid);
+  const int64_t grid_rows = round_up(num_rows, 128) / kRowsPerBlock;
+  const int64_t grid_cols = ceil_div(sc_pad, kColsPerBlock);
+  CK_REQUIRE(grid_rows <= 0x7FFFFFFF && grid_cols <= 65535, "quantize_nvfp4: tensor too large for one launch");
+  const dim3 grid(static_cast<unsigned>(grid_rows), static_cast<unsigned>(grid_cols)), block(kColsPerBlock, kRowsPerBlock);
   // vector path: every 16-element run is inside the input and 32-byte aligned
   const bool vec = (orig_rows == num_rows) && (orig_cols == num_cols) &&
                    (reinterpret_cast<uintptr_t>(input) % 32 == 0);
@@ -323,8 +324,8 @@ int launch_nvfp4(const void* input, const float* gs, void* codes, void* scales, 
   uint8_t* s = static_cast<uint8_t*>(scales);
   const bool exact = use_exact_division();
 #define CK_LAUNCH(VEC, FAST)                                                                          \
-  quantize_nvfp4_kernel<T, VEC, FAST><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(          \
-      x, gs, c, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, total, hi_first)
+  quantize_nvfp4_kernel<T, VEC, FAST><<<grid, block, 0, stream>>>(                                    \
+      x, gs, c, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, hi_first)
   if (vec) {
     if (exact) CK_LAUNCH(true, false); else CK_LAUNCH(true, true);
   } else {
@@ -339,21 +340,22 @@ template <typename T>
 int launch_mxfp8(const void* input, void* data, void* scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
                  int64_t num_cols, cudaStream_t stream) {
   const int64_t sc_pad = round_up(num_cols / 32, 4);
-  const int64_t total = round_up(num_rows, 128) * sc_pad;
-  const int64_t grid = ceil_div(total, kThreads);
-  CK_REQUIRE(grid <= 0x7FFFFFFF, "quantize_mxfp8: tensor too large (%lld blocks)", (long long)grid);
+  const int64_t grid_rows = round_up(num_rows, 128) / kRowsPerBlock;
+  const int64_t grid_cols = ceil_div(sc_pad, kColsPerBlock);
+  CK_REQUIRE(grid_rows <= 0x7FFFFFFF && grid_cols <= 65535, "quantize_mxfp8: tensor too large for one launch");
+  const dim3 grid(static_cast<unsigned>(grid_rows), static_cast<unsigned>(grid_cols)), block(kColsPerBlock, kRowsPerBlock);
   const bool vec = (orig_rows == num_rows) && (orig_cols == num_cols) &&
                    (reinterpret_cast<uintptr_t>(input) % 32 == 0) && (reinterpret_cast<uintptr_t>(data) % 32 == 0);
   const T* x = static_cast<const T*>(input);
   uint8_t* d = static_cast<uint8_t*>(data);
   uint8_t* s = static_cast<uint8_t*>(scales);
   if (vec) {
-    quantize_mxfp8_kernel<T, true><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-        x, d, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, total);
+    quantize_mxfp8_kernel<T, true><<<grid, block, 0, stream>>>(x, d, s, orig_rows, orig_cols, num_rows, num_cols,
+                                                               sc_pad);
   } else {
     CK_REQUIRE(reinterpret_cast<uintptr_t>(data) % 32 == 0, "quantize_mxfp8: output must be 32-byte aligned");
-    quantize_mxfp8_kernel<T, false><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-        x, d, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, total);
+    quantize_mxfp8_kernel<T, false><<<grid, block, 0, stream>>>(x, d, s, orig_rows, orig_cols, num_rows, num_cols,
+                                                                sc_pad);
   }
   CK_CUDA(cudaGetLastError());
   return CK_OK;

@@ -147,8 +147,9 @@ def test_quotients_at_rounding_thresholds(ck, cuda_device):
         row[8:15] = -thresholds * blk_scale
         rows.append(row)
     base = torch.stack(rows).bfloat16()
-    up = (base.view(torch.int16) + 1).view(torch.bfloat16)
-    down = (base.view(torch.int16) - 1).view(torch.bfloat16)
+    nonzero = base != 0  # stepping the bits of 0.0 down would make a NaN
+    up = torch.where(nonzero, (base.view(torch.int16) + 1).view(torch.bfloat16), base)
+    down = torch.where(nonzero, (base.view(torch.int16) - 1).view(torch.bfloat16), base)
     x = torch.cat([base, up, down], dim=0)
     x = torch.cat([x, torch.zeros(16 - x.shape[0] % 16, 16, dtype=torch.bfloat16)], dim=0) if x.shape[0] % 16 else x
     for gs in [1.0, 1.0 / 3.0, 0.0071]:
