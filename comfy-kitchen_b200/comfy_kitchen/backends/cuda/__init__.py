@@ -20,6 +20,8 @@ from comfy_kitchen.ops import DTYPE_TO_CODE
 __all__ = [
     "quantize_nvfp4",
     "quantize_mxfp8",
+    "dequantize_nvfp4",
+    "dequantize_mxfp8",
     "scaled_mm_nvfp4",
     "scaled_mm_mxfp8",
 ]
@@ -46,6 +48,9 @@ _SIGNATURES = {
     "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_gemm_status": [_P],
+    "ck_debug_resident_pairs": [],
+    "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],
+    "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
 }
 _RESTYPE = {"ck_last_error": ctypes.c_char_p}
 
@@ -155,6 +160,40 @@ def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor
     return qx.view(torch.float8_e4m3fn), sx.view(torch.float8_e8m0fnu)
 
 
+def dequantize_nvfp4(qx: torch.Tensor, per_tensor_scale: torch.Tensor, block_scales: torch.Tensor,
+                     output_type: torch.dtype = torch.bfloat16, hi_first: bool = True) -> torch.Tensor:
+    """uint8 [M, K/2] codes + swizzled E4M3 scales + fp32 tensor scale -> [M, K] of ``output_type``."""
+    lib = load_library()
+    qx, block_scales = _plain(qx), _plain(block_scales)
+    assert qx.is_contiguous() and block_scales.is_contiguous(), "Input tensor must be contiguous"
+    rows, packed = qx.shape
+    cols = packed * 2
+    assert cols % 16 == 0, f"num_cols must be divisible by 16, got {cols}"
+    assert tuple(block_scales.shape) == (roundup(rows, 128), roundup(cols // 16, 4)), "Invalid scale shape"
+    scale = _scalar_f32(per_tensor_scale, qx.device, "per_tensor_scale")
+    out = torch.empty((rows, cols), device=qx.device, dtype=output_type)
+    with torch.cuda.device(qx.device):
+        _check(lib.ck_dequantize_nvfp4(_ptr(qx), _ptr(scale), _ptr(block_scales), _ptr(out), DTYPE_TO_CODE[output_type],
+                                       rows, cols, int(bool(hi_first)), _stream(qx.device)), "dequantize_nvfp4")
+    return out
+
+
+def dequantize_mxfp8(qx: torch.Tensor, block_scales: torch.Tensor,
+                     output_type: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """float8_e4m3fn [M, K] + swizzled E8M0 scales -> [M, K] of ``output_type``."""
+    lib = load_library()
+    qx, block_scales = _plain(qx), _plain(block_scales)
+    assert qx.is_contiguous() and block_scales.is_contiguous(), "Input tensor must be contiguous"
+    rows, cols = qx.shape
+    assert cols % 32 == 0, f"num_cols must be divisible by 32, got {cols}"
+    assert tuple(block_scales.shape) == (roundup(rows, 128), roundup(cols // 32, 4)), "Invalid scale shape"
+    out = torch.empty((rows, cols), device=qx.device, dtype=output_type)
+    with torch.cuda.device(qx.device):
+        _check(lib.ck_dequantize_mxfp8(_ptr(qx), _ptr(block_scales), _ptr(out), DTYPE_TO_CODE[output_type], rows, cols,
+                                       _stream(qx.device)), "dequantize_mxfp8")
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 # GEMMs
 # ------------------------------------------------------------------------------------------
@@ -248,6 +287,17 @@ def _build_constraints() -> dict:
             default_devices=cuda_only, min_compute_capability=blackwell),
         "quantize_mxfp8": FunctionConstraints(
             params={"x": ParamConstraint(dtypes=floats, shape_rules=(ExactDims(2),))},
+            default_devices=cuda_only, min_compute_capability=blackwell),
+        "dequantize_nvfp4": FunctionConstraints(
+            params={"qx": ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=(ExactDims(2),)),
+                    "per_tensor_scale": ParamConstraint(dtypes=f32),
+                    "block_scales": ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn})),
+                    "output_type": ParamConstraint(dtypes=floats)},
+            default_devices=cuda_only, min_compute_capability=blackwell),
+        "dequantize_mxfp8": FunctionConstraints(
+            params={"qx": ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn}), shape_rules=(ExactDims(2), DivisibleBy(1, 32))),
+                    "block_scales": ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                    "output_type": ParamConstraint(dtypes=floats)},
             default_devices=cuda_only, min_compute_capability=blackwell),
         "scaled_mm_nvfp4": FunctionConstraints(
             params={"a": ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=(ExactDims(2), DivisibleBy(1, 16))),

@@ -1,0 +1,95 @@
+"""What the two block-scaled tensor-core layouts (NVFP4, MXFP8) have in common.
+
+Both pad a 2-D tensor to a multiple of their block granule, keep a ``transposed`` flag
+instead of moving bytes on ``.t()``, and route ``linear`` / ``mm`` (and for MXFP8 ``addmm``)
+to one ``scaled_mm`` kernel that computes ``a @ b_physical.T``; every other configuration
+dequantizes and runs the dense op.  The handler logic of the reference
+(comfy_kitchen/tensor/nvfp4.py:124-264, comfy_kitchen/tensor/mxfp8.py:105-236) is written
+once here and parameterised by the layout.
+"""
+from __future__ import annotations
+
+import logging
+import os
+
+import torch
+
+from .base import QuantizedTensor, dequantize_args, register_layout_op
+
+logger = logging.getLogger(__name__)
+
+
+def strict_mode() -> bool:
+    """CK_STRICT=1: a failing fast path raises instead of silently falling back to dequantization."""
+    return os.environ.get("CK_STRICT", "0") == "1"
+
+
+def crop(result: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """Cut a padded matmul result back to the logical output shape."""
+    if result.shape[0] != rows or result.shape[1] != cols:
+        return result[:rows, :cols]
+    return result
+
+
+def _is_transposed(t) -> bool:
+    return getattr(t._params, "transposed", False)
+
+
+def _both_quantized_2d(a, b) -> bool:
+    return isinstance(a, QuantizedTensor) and isinstance(b, QuantizedTensor) and a._qdata.dim() == 2
+
+
+def install_handlers(layout, *, name: str, with_addmm: bool) -> None:
+    """Register the aten.t / mm / linear (/ addmm) handlers of a block-scaled layout.
+
+    ``layout.scaled_mm(a, b, bias, out_dtype)`` runs the fused kernel on two QuantizedTensors.
+    """
+
+    def fast(dense_op, dense_args, a, b, bias, out_dtype, rows, cols, what):
+        try:
+            return crop(layout.scaled_mm(a, b, bias, out_dtype), rows, cols)
+        except (RuntimeError, TypeError) as e:
+            if strict_mode():
+                raise
+            logger.warning(f"{name} {what} failed: {e}, falling back to dequantization")
+            return dense_op(*dequantize_args(dense_args))
+
+    @register_layout_op(torch.ops.aten.t.default, layout)
+    def _transpose(qt, args, kwargs):
+        # no bytes move: the logical shape is swapped and the flag flipped
+        src = args[0]
+        if not isinstance(src, QuantizedTensor):
+            return torch.ops.aten.t.default(*args, **kwargs)
+        rows, cols = src._params.orig_shape
+        params = layout.params_like(src._params, orig_shape=(cols, rows), transposed=not _is_transposed(src))
+        return QuantizedTensor(src._qdata, layout.__name__, params)
+
+    @register_layout_op(torch.ops.aten.mm.default, layout)
+    def _mm(qt, args, kwargs):
+        # a @ b is the kernel's a @ b_physical.T exactly when b carries a deferred transpose
+        # (the torch.compile decomposition linear(x, w) -> mm(x, w.t()))
+        a, b = args[0], args[1]
+        if not _both_quantized_2d(a, b) or _is_transposed(a) or not _is_transposed(b):
+            return torch.mm(*dequantize_args(args))
+        out_dtype = kwargs.get("out_dtype", a._params.orig_dtype)
+        return fast(torch.mm, args, a, b, None, out_dtype, a._params.orig_shape[0], b._params.orig_shape[1], "mm")
+
+    @register_layout_op(torch.ops.aten.linear.default, layout)
+    def _linear(qt, args, kwargs):
+        x, w = args[0], args[1]
+        bias = args[2] if len(args) > 2 else None
+        dense_args = (x, w, bias)
+        if not _both_quantized_2d(x, w) or _is_transposed(x) or _is_transposed(w):
+            return torch.nn.functional.linear(*dequantize_args(dense_args))
+        out_dtype = kwargs.get("out_dtype", x._params.orig_dtype)
+        return fast(torch.nn.functional.linear, dense_args, x, w, bias, out_dtype, x._params.orig_shape[0],
+                    w._params.orig_shape[0], "scaled_mm")
+
+    if with_addmm:
+        @register_layout_op(torch.ops.aten.addmm.default, layout)
+        def _addmm(qt, args, kwargs):
+            bias, a, b = args[0], args[1], args[2]
+            if not _both_quantized_2d(a, b) or _is_transposed(a) or not _is_transposed(b):
+                return torch.addmm(*dequantize_args((bias, a, b)))
+            return fast(torch.addmm, (bias, a, b), a, b, bias, a._params.orig_dtype, a._params.orig_shape[0],
+                        b._params.orig_shape[1], "addmm")

@@ -102,6 +102,26 @@ CK_API int ck_quantize_mxfp8(const void* input, int input_dtype,
                       void* stream);
 
 /*
+ * NVFP4 dequantization: packed codes uint8 [rows, cols/2] + swizzled E4M3 block
+ * scales + one fp32 tensor scale -> [rows, cols] of out_dtype (f32/f16/bf16).
+ * The arithmetic is done in the output dtype exactly as
+ * comfy_kitchen/backends/eager/quantization.py:171-219 does.  cols % 16 == 0.
+ * Replaces launch_dequantize_nvfp4_kernel,
+ * comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:386-435.
+ */
+CK_API int ck_dequantize_nvfp4(const void* codes, const float* global_scale, const void* block_scales,
+                        void* out, int out_dtype, int64_t rows, int64_t cols, int hi_first, void* stream);
+
+/*
+ * MXFP8 dequantization: E4M3 bytes [rows, cols] + swizzled E8M0 block scales ->
+ * [rows, cols] of out_dtype, float32 arithmetic then one cast
+ * (comfy_kitchen/backends/eager/quantization.py:327-364; the reference has no
+ * native kernel for this operator).  cols % 32 == 0.
+ */
+CK_API int ck_dequantize_mxfp8(const void* data, const void* block_scales, void* out, int out_dtype,
+                        int64_t rows, int64_t cols, void* stream);
+
+/*
  * NVFP4 GEMM with linear semantics:
  *   out[M,N] = cast( (deq(a)[M,K] . deq(b)[N,K]^T) * alpha + bias[N] )
  * a: uint8 [M, K/2], b: uint8 [N, K/2] packed E2M1 (both operands with the same

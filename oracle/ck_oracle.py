@@ -223,14 +223,34 @@ def quantize_nvfp4(x, per_tensor_scale, pad_16x: bool = False, hi_first: bool = 
     return pack_fp4(codes, hi_first), to_blocked(s8)           # :158-159
 
 
-def dequantize_nvfp4(packed, per_tensor_scale, blocked_scales, hi_first: bool = True):
-    """NVFP4 -> float32 (eager/quantization.py:171-219 with output_type=float32)."""
+def round_to_dtype(x: np.ndarray, out_dtype: str) -> np.ndarray:
+    """float32 values rounded (nearest-even) to "float32" | "float16" | "bfloat16", returned as float32."""
+    x = np.asarray(x, dtype=np.float32)
+    if out_dtype == "float32":
+        return x
+    if out_dtype == "float16":
+        with np.errstate(over="ignore"):
+            return x.astype(np.float16).astype(np.float32)
+    if out_dtype == "bfloat16":
+        return bf16_bits_to_f32(f32_to_bf16_bits(x))
+    raise ValueError(out_dtype)
+
+
+def dequantize_nvfp4(packed, per_tensor_scale, blocked_scales, hi_first: bool = True, out_dtype: str = "float32"):
+    """NVFP4 -> values of ``out_dtype`` (returned as float32), eager/quantization.py:171-219.
+
+    The reference does the arithmetic in the output dtype: the tensor scale and the
+    block scale are cast to it, multiplied (:211), and the product scales the code
+    value (:214); each product of two output-dtype numbers is exact in float32, so
+    rounding the float32 product reproduces the output-dtype multiplication.
+    """
     codes = unpack_fp4(np.asarray(packed, dtype=np.uint8), hi_first)
     rows, cols = codes.shape
     s8 = from_blocked(np.asarray(blocked_scales, dtype=np.uint8), rows, cols // 16)
-    total = np.float32(per_tensor_scale) * e4m3_to_f32(s8)     # :211
+    ts = round_to_dtype(np.float32(per_tensor_scale), out_dtype)
+    total = round_to_dtype(ts * e4m3_to_f32(s8), out_dtype)    # :211
     vals = E2M1_VALUES[codes].reshape(rows, cols // 16, 16)
-    return (vals * total[..., None]).reshape(rows, cols).astype(np.float32)
+    return round_to_dtype((vals * total[..., None]).reshape(rows, cols), out_dtype)
 
 
 # --------------------------------------------------------------------------- #
@@ -286,13 +306,16 @@ def quantize_mxfp8(x, pad_32x: bool = False):
     return data, to_blocked(e)                                       # :322-324
 
 
-def dequantize_mxfp8(data, blocked_scales):
-    """MXFP8 -> float32 (eager/quantization.py:327-364 with output_type=float32)."""
+def dequantize_mxfp8(data, blocked_scales, out_dtype: str = "float32"):
+    """MXFP8 -> values of ``out_dtype`` (returned as float32), eager/quantization.py:327-364:
+    float32 product, then one cast."""
     data = np.asarray(data, dtype=np.uint8)
     rows, cols = data.shape
     e = from_blocked(np.asarray(blocked_scales, dtype=np.uint8), rows, cols // 32)
     vals = e4m3_to_f32(data).reshape(rows, cols // 32, 32)
-    return (vals * e8m0_to_f32(e)[..., None]).reshape(rows, cols).astype(np.float32)
+    with np.errstate(invalid="ignore"):
+        prod = (vals * e8m0_to_f32(e)[..., None]).reshape(rows, cols).astype(np.float32)
+    return round_to_dtype(prod, out_dtype)
 
 
 # --------------------------------------------------------------------------- #

@@ -55,6 +55,8 @@ def main(ref_root: str) -> None:
         out[name] = dict(
             x=_bits(x), x_dtype=str(x.dtype).replace("torch.", ""), scale=np.float32(scale.item()),
             pad=pad, hi_first=hi_first, codes=_bits(q), scales=_bits(s), deq=_bits(deq),
+            deq_bf16=_bits(ck.dequantize_nvfp4(q, scale, s, torch.bfloat16, hi_first=hi_first)),
+            deq_f16=_bits(ck.dequantize_nvfp4(q, scale, s, torch.float16, hi_first=hi_first)),
         )
         return q, s, scale
 
@@ -64,6 +66,8 @@ def main(ref_root: str) -> None:
         out[name] = dict(
             x=_bits(x), x_dtype=str(x.dtype).replace("torch.", ""), pad=pad,
             data=_bits(q), scales=_bits(s), deq=_bits(deq),
+            deq_bf16=_bits(ck.dequantize_mxfp8(q, s, torch.bfloat16)),
+            deq_f16=_bits(ck.dequantize_mxfp8(q, s, torch.float16)),
         )
         return q, s
 

@@ -26,11 +26,20 @@ def test_quantize_nvfp4_matches_reference(name):
     np.testing.assert_array_equal(codes, d["codes"])
 
 
+def _golden_as_f32(bits16: np.ndarray, kind: str) -> np.ndarray:
+    if kind == "bfloat16":
+        return oc.bf16_bits_to_f32(bits16)
+    return bits16.view(np.float16).astype(np.float32)
+
+
 @pytest.mark.parametrize("name", golden_names("nvfp4_"))
 def test_dequantize_nvfp4_matches_reference(name):
     d = load_golden(name)
     deq = oc.dequantize_nvfp4(d["codes"], d["scale"], d["scales"], hi_first=bool(d["hi_first"]))
     np.testing.assert_array_equal(deq.view(np.uint32), d["deq"].view(np.uint32))
+    for key, kind in (("deq_bf16", "bfloat16"), ("deq_f16", "float16")):
+        got = oc.dequantize_nvfp4(d["codes"], d["scale"], d["scales"], hi_first=bool(d["hi_first"]), out_dtype=kind)
+        np.testing.assert_array_equal(got.view(np.uint32), _golden_as_f32(d[key], kind).view(np.uint32))
 
 
 @pytest.mark.parametrize("name", golden_names("mxfp8_"))
@@ -47,6 +56,9 @@ def test_dequantize_mxfp8_matches_reference(name):
     d = load_golden(name)
     deq = oc.dequantize_mxfp8(d["data"], d["scales"])
     np.testing.assert_array_equal(deq.view(np.uint32), d["deq"].view(np.uint32))
+    for key, kind in (("deq_bf16", "bfloat16"), ("deq_f16", "float16")):
+        got = oc.dequantize_mxfp8(d["data"], d["scales"], out_dtype=kind)
+        np.testing.assert_array_equal(got.view(np.uint32), _golden_as_f32(d[key], kind).view(np.uint32))
 
 
 @pytest.mark.parametrize("name", golden_names("swizzle_"))
