@@ -310,6 +310,68 @@ def run_e2e(torch, ck, wl: Workload, steps: int, warmup: int, dist=None) -> dict
     return {"ms": ms, "h2d": wl.x_host.numel() * 2, "d2h": out_host.numel() * 2}
 
 
+def run_sharded_gemm(args, torch, ck, dist, device, rank, world, clocks_cls, local_rank) -> dict | None:
+    """NVFP4 GEMM with N column-sharded over the ranks and an NCCL all-gather of the bf16 output.
+
+    Strong scaling: the problem is fixed, each rank computes y[:, shard].  Two timings: the local
+    GEMM alone (aggregate TFLOP/s scales with the ranks) and GEMM + all-gather (bounded by the
+    NVLink bytes each rank receives: (g-1)/g * 2*M*N)."""
+    from comfy_kitchen import sharded
+
+    m, n, k = (int(v) for v in args.shape.split(","))
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(m, k, generator=g).bfloat16().to(device)
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(device)
+    sx = (x.abs().amax() / 2688.0).float()
+    sw = (w.abs().amax() / 2688.0).float()
+    qx, bsx = ck.quantize_nvfp4(x, sx)
+    qw, bsw = ck.quantize_nvfp4(w, sw)
+    shard = sharded.ShardedQuantizedWeight.from_full(qw, bsw, sw, None, world, rank)
+    del w, qw, bsw
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with clocks_cls(local_rank) as clocks:
+        ms_gemm = timed(lambda: sharded.sharded_linear_nvfp4(qx, sx, bsx, shard, gather=False), args.steps, args.warmup)
+        ms_full = timed(lambda: sharded.sharded_linear_nvfp4(qx, sx, bsx, shard), args.steps, args.warmup)
+    y = sharded.sharded_linear_nvfp4(qx, sx, bsx, shard)
+    y_local = sharded.sharded_linear_nvfp4(qx, sx, bsx, shard, gather=False)
+    ok = bool(torch.equal(y[:, shard.start:shard.end], y_local)) and tuple(y.shape) == (m, n)
+    if rank != 0:
+        return None
+    flops = 2.0 * m * n * k
+    recv = (world - 1) / world * 2.0 * m * n
+    return {
+        "metric": "sharded_nvfp4_gemm_tflops", "value": flops / (ms_full * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"NVFP4 GEMM M={m} N={n} K={k}, N column-sharded over {world} GPUs + NCCL all-gather of bf16 output",
+                   "M": m, "N": n, "K": k},
+        "gemm_only": {"ms": ms_gemm, "aggregate_tflops": flops / (ms_gemm * 1e-3) / 1e12},
+        "all_gather": {"bytes_received_per_gpu": recv, "ms": max(ms_full - ms_gemm, 0.0),
+                       "gbs_per_gpu": (recv / ((ms_full - ms_gemm) * 1e-3) / 1e9) if ms_full > ms_gemm else None,
+                       "nvlink_peak_gbs": 770.0},
+        "gathered_equals_local": ok, "clocks": clocks.summary(), "gpu_launches": args.steps,
+    }
+
+
 def run_gpu_arm(args) -> dict | None:
     import torch
 
@@ -336,6 +398,11 @@ def run_gpu_arm(args) -> dict | None:
         raise SystemExit(f"cuda backend unavailable: {info['unavailable_reason']}")
     lib = backend.load_library()
     peaks, peak_kind = load_peaks()
+    if args.case == "sharded_gemm":
+        line = run_sharded_gemm(args, torch, ck, dist, device, rank, world, ClockSampler, local_rank)
+        if dist is not None:
+            dist.destroy_process_group()
+        return line
 
     rows = args.rows or M
     ring = args.ring
@@ -462,7 +529,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="linear",
-                    choices=["linear", "linear_mxfp8", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8"])
+                    choices=["linear", "linear_mxfp8", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
+                             "sharded_gemm"])
+    ap.add_argument("--shape", default="16384,15360,3072", help="M,N,K of --case sharded_gemm")
     ap.add_argument("--rows", type=int, default=0, help="override M (profiling of one kernel on a different size)")
     ap.add_argument("--ring", type=int, default=8, help="independent buffer sets cycled through (L2 defeat)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
