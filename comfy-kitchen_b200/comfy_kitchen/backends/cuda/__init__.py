@@ -24,6 +24,7 @@ __all__ = [
     "dequantize_mxfp8",
     "scaled_mm_nvfp4",
     "scaled_mm_mxfp8",
+    "linear_nvfp4_fused",
 ]
 
 _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
@@ -48,6 +49,7 @@ _SIGNATURES = {
     "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_gemm_status": [_P],
+    "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
     "ck_debug_resident_pairs": [],
     "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],
     "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
@@ -243,6 +245,54 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
                                       _stream(dev)), "scaled_mm_nvfp4")
     del bias_keep
     return out
+
+
+ACTIVATIONS = {None: 0, "none": 0, "gelu_tanh": 1}
+
+
+def linear_nvfp4_fused(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tensor, tensor_scale_b: torch.Tensor,
+                       block_scale_a: torch.Tensor, block_scale_b: torch.Tensor, bias: torch.Tensor | None = None,
+                       activation: str | None = None, out_dtype: torch.dtype | None = None,
+                       requant_scale: torch.Tensor | None = None, return_dense: bool = True):
+    """NVFP4 linear whose epilogue applies ``activation`` and, when ``requant_scale`` (a static
+    per-tensor scale) is given, quantizes the result to NVFP4 for the next layer.
+
+    Returns ``(h, codes, block_scales)``: ``h`` is the dense [M, N] output (None when
+    ``return_dense`` is False), ``codes`` / ``block_scales`` are what
+    ``quantize_nvfp4(h, requant_scale)`` would return (None without ``requant_scale``).
+    No counterpart in the reference, which runs the three steps as separate kernels.
+    """
+    lib = load_library()
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    out_dtype = out_dtype or torch.bfloat16
+    m, ka = a.shape
+    n, kb = b.shape
+    assert ka == kb, "Matrix dimensions do not match"
+    k = 2 * ka
+    sk = roundup(k // 16, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    assert activation in ACTIVATIONS, f"unknown activation {activation!r}"
+    assert return_dense or requant_scale is not None, "nothing to compute"
+    dev = a.device
+    tsa = _scalar_f32(tensor_scale_a, dev, "tensor_scale_a")
+    tsb = _scalar_f32(tensor_scale_b, dev, "tensor_scale_b")
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    out = torch.empty((m, n), dtype=out_dtype, device=dev) if return_dense else None
+    codes = scales = rq = None
+    if requant_scale is not None:
+        assert n % 64 == 0, "re-quantized output needs N % 64 == 0"
+        rq = _scalar_f32(requant_scale, dev, "requant_scale")
+        codes = torch.empty((m, n // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty((roundup(m, 128), n // 16), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib.ck_linear_nvfp4_fused(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa), _ptr(tsb),
+                                         None, bias_ptr, bias_code, ACTIVATIONS[activation], _ptr(out),
+                                         DTYPE_TO_CODE[out_dtype], _ptr(codes), _ptr(scales), _ptr(rq), m, n, k,
+                                         _stream(dev)), "linear_nvfp4_fused")
+    del bias_keep
+    return out, codes, None if scales is None else scales.view(torch.float8_e4m3fn)
 
 
 def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,

@@ -21,6 +21,7 @@
 // All synchronisation is by mbarriers with bounded waits (ck_sm100.cuh): a protocol error
 // raises the device status word instead of hanging.
 #include "ck_sm100.cuh"
+#include "ck_quant_math.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -104,18 +105,19 @@ struct GemmParams {
   int n_row_blocks_b;      // ceil(N / 128)
   int tiles_m, tiles_n;
   int* status;             // device status word: set non-zero when a wait gave up
+  // fused epilogue (FUSED kernels only)
+  int activation;          // CK_ACT_*
+  uint8_t* rq_codes;       // [M, N/2] NVFP4 codes of the (activated) output, or null
+  uint8_t* rq_scales;      // its tiled E4M3 block scales, [roundup(M,128), N/16]
+  const float* rq_scale;   // its per-tensor scale (device)
 };
 
 __device__ int g_gemm_status = 0;
 
-// 32 consecutive output columns of one row: scale, add bias, convert, store.
-// `bias_s` points at the 32 fp32 bias values of these columns in shared memory (all lanes
-// read the same addresses: broadcast).  `vec_ok`: the row pitch and column offset allow
-// 32-byte aligned vector stores.
-template <typename OutT>
-__device__ __forceinline__ void finish_row_chunk(OutT* dst, const uint32_t (&raw)[32], float alpha,
-                                                 const float* bias_s, int valid, bool vec_ok) {
-  float v[32];
+// alpha * acc + bias for 32 consecutive output columns of one row.  `bias_s` points at the 32
+// fp32 bias values of these columns in shared memory (all lanes read the same addresses).
+__device__ __forceinline__ void scale_and_bias(const uint32_t (&raw)[32], float alpha, const float* bias_s,
+                                               float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const float4 b = reinterpret_cast<const float4*>(bias_s)[i];
@@ -124,6 +126,12 @@ __device__ __forceinline__ void finish_row_chunk(OutT* dst, const uint32_t (&raw
     v[4 * i + 2] = fmaf(__uint_as_float(raw[4 * i + 2]), alpha, b.z);
     v[4 * i + 3] = fmaf(__uint_as_float(raw[4 * i + 3]), alpha, b.w);
   }
+}
+
+// Convert and store 32 consecutive output columns of one row.  `vec_ok`: the row pitch and
+// column offset allow 32-byte aligned vector stores.
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[32], int valid, bool vec_ok) {
   if (valid == 32 && vec_ok) {
     if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
@@ -166,13 +174,33 @@ __device__ __forceinline__ void finish_row_chunk(OutT* dst, const uint32_t (&raw
   }
 }
 
+template <typename OutT>
+__device__ __forceinline__ float round_to_out(float x) {
+  if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+  } else if constexpr (std::is_same<OutT, __half>::value) {
+    return __half2float(__float2half_rn(x));
+  } else {
+    return x;
+  }
+}
+
+// tanh-approximated GELU in fp32: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(inner));
+}
+
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
   if (dtype == CK_DTYPE_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
   if (dtype == CK_DTYPE_F16) return __half2float(static_cast<const __half*>(bias)[n]);
   return static_cast<const float*>(bias)[n];
 }
 
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT>
+// FUSED: the epilogue applies an activation to the output rounded to OutT (what an unfused
+// caller would see), optionally stores it, and optionally re-quantizes it to NVFP4 (codes +
+// tiled block scales against a static per-tensor scale) as the A operand of the next GEMM.
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED>
 __global__ void __launch_bounds__(kNumThreads, 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -443,11 +471,63 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
       }
       OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0 + c0;
+      if constexpr (!FUSED) {
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        const int valid = min(32, p.N - (n0 + c0 + c * 32));
-        if (row < p.M && valid > 0) {
-          finish_row_chunk<OutT>(out_row + c * 32, buf[c], alpha, bias_s + c0 + c * 32, valid, vec_ok);
+        for (int c = 0; c < kChunks; ++c) {
+          const int valid = min(32, p.N - (n0 + c0 + c * 32));
+          if (row < p.M && valid > 0) {
+            float v[32];
+            scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
+            store_row_chunk<OutT>(out_row + c * 32, v, valid, vec_ok);
+          }
+        }
+      } else {
+        // Re-quantization needs whole 64-column groups (4 scale columns = one 32-bit word of
+        // the tiled scale layout); the host guarantees N % 64 == 0 when it is requested.
+        static_assert(kChunks % 2 == 0, "fused epilogue works on pairs of 32-column chunks");
+        const float rq_g = (p.rq_codes != nullptr) ? __ldg(p.rq_scale) : 1.0f;
+        const int rq_col_tiles = (p.N / 16 + 3) / 4;
+        const int rows_pad = (p.M + 127) / 128 * 128;
+        uint32_t scale_word = 0;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const int col = n0 + c0 + c * 32;
+          const int valid = min(32, p.N - col);
+          if (valid <= 0) continue;
+          float v[32];
+          if (row < p.M) {
+            scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float y = round_to_out<OutT>(v[i]);
+              if (p.activation == CK_ACT_GELU_TANH) y = round_to_out<OutT>(gelu_tanh(y));
+              v[i] = y;
+            }
+            if (p.out != nullptr) store_row_chunk<OutT>(out_row + c * 32, v, valid, vec_ok);
+          }
+          if (p.rq_codes != nullptr) {
+            if (row < p.M) {
+              float lo16[16], hi16[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                lo16[i] = v[i];
+                hi16[i] = v[16 + i];
+              }
+              uint32_t w0, w1, w2, w3, s0, s1;
+              quant::nvfp4_block<true>(lo16, rq_g, true, w0, w1, s0);
+              quant::nvfp4_block<true>(hi16, rq_g, true, w2, w3, s1);
+              *reinterpret_cast<uint4*>(p.rq_codes + static_cast<int64_t>(row) * (p.N >> 1) + (col >> 1)) =
+                  make_uint4(w0, w1, w2, w3);
+              scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
+            }
+            if ((c & 1) && row < rows_pad) {
+              // rows between M and the next multiple of 128 are padding of the scale tensor: zero
+              // this chunk and the previous one cover scale columns (col/16 - 2) .. (col/16 + 1)
+              const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
+              *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
+              scale_word = 0;
+            }
+          }
         }
       }
     }
@@ -521,10 +601,10 @@ int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64
   return CK_OK;
 }
 
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT>
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED>
 int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, cudaStream_t stream) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
-  auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT>;
+  auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT, FUSED>;
   // the dynamic shared-memory opt-in is per device: do it once for each device that launches
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -579,7 +659,7 @@ int forced_config() {
   return e ? atoi(e) : 0;
 }
 
-template <Kind KIND, typename OutT>
+template <Kind KIND, typename OutT, bool FUSED>
 int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[3], const GemmParams& p,
                      cudaStream_t stream) {
   // map_b[0|1|2] have boxes of 128 | 192 | 256 rows.
@@ -597,21 +677,42 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[3], co
   }
   switch (config) {
     case 4:
-      return launch_config<KIND, 256, 1, 5, 2, OutT>(map_a, map_b[0], p, stream);
+      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED>(map_a, map_b[0], p, stream);
     case 3:
-      return launch_config<KIND, 256, 1, 4, 1, OutT>(map_a, map_b[2], p, stream);
+      return launch_config<KIND, 256, 1, 4, 1, OutT, FUSED>(map_a, map_b[2], p, stream);
     case 2:
-      return launch_config<KIND, 192, 2, 4, 1, OutT>(map_a, map_b[1], p, stream);
+      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 4, 1, OutT, false>(map_a, map_b[1], p, stream);
+      [[fallthrough]];  // the fused epilogue needs 64-column warp shares: no 192-wide variant
     default:
-      return launch_config<KIND, 128, 2, 6, 1, OutT>(map_a, map_b[0], p, stream);
+      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, stream);
   }
 }
+
+struct FusedArgs {
+  bool enabled = false;
+  int activation = CK_ACT_NONE;
+  void* rq_codes = nullptr;
+  void* rq_scales = nullptr;
+  const float* rq_scale = nullptr;
+};
 
 template <Kind KIND>
 int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, const void* sfb, const float* tsa,
               const float* tsb, const float* alpha, const void* bias, int bias_dtype, void* out, int out_dtype,
-              int64_t M, int64_t N, int64_t K, void* stream) {
-  CK_REQUIRE(a && b && sfa && sfb && out, "%s: null pointer", op);
+              int64_t M, int64_t N, int64_t K, void* stream, const FusedArgs& fused = FusedArgs()) {
+  CK_REQUIRE(a && b && sfa && sfb, "%s: null pointer", op);
+  CK_REQUIRE(out != nullptr || (fused.enabled && fused.rq_codes != nullptr), "%s: no output requested", op);
+  if (fused.enabled) {
+    CK_REQUIRE(fused.activation == CK_ACT_NONE || fused.activation == CK_ACT_GELU_TANH, "%s: unknown activation %d", op,
+               fused.activation);
+    if (fused.rq_codes != nullptr) {
+      CK_REQUIRE(fused.rq_scales != nullptr && fused.rq_scale != nullptr, "%s: re-quantization needs scales", op);
+      CK_REQUIRE(N % 64 == 0, "%s: re-quantized output needs N %% 64 == 0, got %lld", op, (long long)N);
+      CK_REQUIRE(reinterpret_cast<uintptr_t>(fused.rq_codes) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(fused.rq_scales) % 4 == 0,
+                 "%s: re-quantized outputs must be 16-byte (codes) and 4-byte (scales) aligned", op);
+    }
+  }
   CK_REQUIRE(M > 0 && N > 0 && K > 0, "%s: empty problem M=%lld N=%lld K=%lld", op, (long long)M, (long long)N,
              (long long)K);
   CK_REQUIRE(M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30), "%s: dimension too large", op);
@@ -642,6 +743,10 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.N = static_cast<int>(N);
   p.k_bytes = static_cast<int>(KIND == Kind::kNvfp4 ? K / 2 : K);
   p.sf_col_tiles = static_cast<int>(ceil_div(K / block, 4));
+  p.activation = fused.activation;
+  p.rq_codes = static_cast<uint8_t*>(fused.rq_codes);
+  p.rq_scales = static_cast<uint8_t*>(fused.rq_scales);
+  p.rq_scale = fused.rq_scale;
   p.n_row_blocks_a = static_cast<int>(ceil_div(M, 128));
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
@@ -652,13 +757,25 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   if (int rc = make_operand_map(&map_b[1], b, N, p.k_bytes, 192)) return rc;
   if (int rc = make_operand_map(&map_b[2], b, N, p.k_bytes, 256)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if constexpr (KIND == Kind::kNvfp4) {
+    if (fused.enabled) {
+      switch (out_dtype) {
+        case CK_DTYPE_BF16:
+          return launch_for_shape<KIND, __nv_bfloat16, true>(map_a, map_b, p, s);
+        case CK_DTYPE_F16:
+          return launch_for_shape<KIND, __half, true>(map_a, map_b, p, s);
+        default:
+          return launch_for_shape<KIND, float, true>(map_a, map_b, p, s);
+      }
+    }
+  }
   switch (out_dtype) {
     case CK_DTYPE_BF16:
-      return launch_for_shape<KIND, __nv_bfloat16>(map_a, map_b, p, s);
+      return launch_for_shape<KIND, __nv_bfloat16, false>(map_a, map_b, p, s);
     case CK_DTYPE_F16:
-      return launch_for_shape<KIND, __half>(map_a, map_b, p, s);
+      return launch_for_shape<KIND, __half, false>(map_a, map_b, p, s);
     default:
-      return launch_for_shape<KIND, float>(map_a, map_b, p, s);
+      return launch_for_shape<KIND, float, false>(map_a, map_b, p, s);
   }
 }
 
@@ -680,12 +797,27 @@ extern "C" int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa,
                                          out, out_dtype, M, N, K, stream);
 }
 
+extern "C" int ck_linear_nvfp4_fused(const void* a, const void* b, const void* sfa, const void* sfb,
+                                     const float* tensor_scale_a, const float* tensor_scale_b, const float* alpha,
+                                     const void* bias, int bias_dtype, int activation, void* out, int out_dtype,
+                                     void* requant_codes, void* requant_block_scales, const float* requant_scale,
+                                     int64_t M, int64_t N, int64_t K, void* stream) {
+  ck::FusedArgs f;
+  f.enabled = true;
+  f.activation = activation;
+  f.rq_codes = requant_codes;
+  f.rq_scales = requant_block_scales;
+  f.rq_scale = requant_scale;
+  return ck::scaled_mm<ck::Kind::kNvfp4>("linear_nvfp4_fused", a, b, sfa, sfb, tensor_scale_a, tensor_scale_b, alpha, bias,
+                                         bias_dtype, out, out_dtype, M, N, K, stream, f);
+}
+
 // Number of CTA pairs the 256x256 configuration runs concurrently on the current device
 // (diagnostic; 0 until that configuration has launched once).
 extern "C" int ck_debug_resident_pairs(void) {
   cudaLaunchConfig_t cfg = {};
   using Cfg = ck::Config<ck::Kind::kNvfp4, 256, 1, 5, 2>;
-  auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16>;
+  auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16, false>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -1;
   cfg.gridDim = dim3(ck::sm_count() / 2 * 2);
   cfg.blockDim = dim3(ck::kNumThreads);

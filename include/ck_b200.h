@@ -142,6 +142,28 @@ CK_API int ck_scaled_mm_nvfp4(const void* a, const void* b, const void* sfa, con
                        int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * NVFP4 linear with a fused epilogue for the next layer:
+ *   y = round_out(deq(a).deq(b)^T * alpha + bias)          (rounded to out_dtype, as an
+ *   h = round_out(act(y))                                    unfused caller would see it)
+ * `out` (nullable) receives h as [M,N] of out_dtype; `requant_codes` (nullable) receives
+ * quantize_nvfp4(h, *requant_scale): packed codes uint8 [M, N/2] (even element in the high
+ * nibble) and E4M3 block scales in the swizzled layout, uint8 [roundup(M,128), N/16],
+ * bit-identical to ck_quantize_nvfp4 applied to h.  Re-quantization needs N % 64 == 0 and a
+ * static per-tensor scale in device memory (the output's amax is unknown until the GEMM
+ * ends; the reference's own model example uses static scales too,
+ * tests/test_integration.py:44-53, samples/nvfp4_linear.py:55-62,79).
+ * activation: CK_ACT_NONE or CK_ACT_GELU_TANH.  Other arguments as ck_scaled_mm_nvfp4.
+ * Fuses the sequence scaled_mm_nvfp4 -> gelu -> quantize_nvfp4 of the reference
+ * (comfy_kitchen/tensor/nvfp4.py:214-264 followed by tensor/nvfp4.py:51-82).
+ */
+CK_API int ck_linear_nvfp4_fused(const void* a, const void* b, const void* sfa, const void* sfb,
+                          const float* tensor_scale_a, const float* tensor_scale_b, const float* alpha,
+                          const void* bias, int bias_dtype, int activation,
+                          void* out, int out_dtype,
+                          void* requant_codes, void* requant_block_scales, const float* requant_scale,
+                          int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
  * MXFP8 GEMM with linear semantics: out[M,N] = cast(deq(a) . deq(b)^T + bias).
  * a: E4M3 bytes [M,K], b: E4M3 bytes [N,K], sfa/sfb: E8M0 block scales in the
  * swizzled layout with roundup(M|N,128) x roundup(K/32,4) bytes.  K must be a
