@@ -42,8 +42,11 @@ constexpr int kTileM = 128;
 constexpr int kStageKBytes = 128;   // bytes of K per operand row per stage (one swizzle atom)
 constexpr int kMmaKBytes = 32;      // bytes of K per tcgen05.mma
 constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
-constexpr int kNumEpilogueWarps = 8;
-constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;  // TMA warp, MMA warp, epilogue warps
+// Epilogue warps per CTA: two per 32-lane quarter of tensor memory for the plain epilogue,
+// four for the fused one (its activation + quantization arithmetic is ~30 instructions per
+// element and must keep up with the tensor pipe).
+constexpr int epilogue_warps(bool fused, int tile_n) { return (fused && tile_n >= 256) ? 16 : 8; }
+constexpr int num_threads(bool fused, int tile_n) { return 64 + 32 * epilogue_warps(fused, tile_n); }  // + TMA, MMA warps
 constexpr int kTmemCols = 512;
 
 // CTAS == 2: a pair of CTAs (a 2-CTA cluster on neighbouring SMs) computes one 256 x TILE_N
@@ -185,10 +188,15 @@ __device__ __forceinline__ float round_to_out(float x) {
   }
 }
 
-// tanh-approximated GELU in fp32: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+// tanh-approximated GELU in fp32: 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3),
+// evaluated as x * sigmoid(2u) = x / (1 + 2^(-2u log2 e)) with the hardware exp2 and
+// reciprocal (relative error ~1e-6, far below the rounding of a 16-bit output type).
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(inner));
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+  float t, r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(t) : "f"(-2.8853900817779268f * u));  // 2^(-2u log2 e) = e^(-2u)
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + t));
+  return x * r;
 }
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
@@ -201,11 +209,12 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
 // caller would see), optionally stores it, and optionally re-quantizes it to NVFP4 (codes +
 // tiled block scales against a static per-tensor scale) as the A operand of the next GEMM.
 template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(num_threads(FUSED, TILE_N), 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                          const GemmParams p) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
+  constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N);
   // In a CTA pair, rank 0 (the leader) issues the MMAs for both CTAs.
   const uint32_t cta_rank = (CTAS == 2) ? cluster_cta_rank() : 0u;
   const int worker = blockIdx.x / CTAS;        // index of this CTA (pair) among the tile workers
@@ -419,8 +428,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // tcgen05.ld, hands the accumulator back to the MMA warp at once, and only then does
     // the arithmetic and the stores - so the next tile's main loop overlaps them.
     const int quarter = warp & 3;  // tensor-memory lanes this warp may read: 32*quarter .. +31
-    const int half = (warp - 2) >> 2;
-    constexpr int kColsPerWarp = TILE_N / 2;
+    const int half = (warp - 2) >> 2;  // which share of the tile's columns
+    constexpr int kColsPerWarp = TILE_N / (kNumEpilogueWarps / 4);
     constexpr int kChunks = kColsPerWarp / 32;
     static_assert(kColsPerWarp % 32 == 0, "tile width must split into 32-column chunks per warp");
     const int et = threadIdx.x - 64;  // 0 .. 32*kNumEpilogueWarps-1 among the epilogue threads
@@ -484,7 +493,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       } else {
         // Re-quantization needs whole 64-column groups (4 scale columns = one 32-bit word of
         // the tiled scale layout); the host guarantees N % 64 == 0 when it is requested.
-        static_assert(kChunks % 2 == 0, "fused epilogue works on pairs of 32-column chunks");
+        static_assert(kChunks % 2 == 0, "fused epilogue works on pairs of 32-column chunks");  // 64-column groups
         const float rq_g = (p.rq_codes != nullptr) ? __ldg(p.rq_scale) : 1.0f;
         const int rq_col_tiles = (p.N / 16 + 3) / 4;
         const int rows_pad = (p.M + 127) / 128 * 128;
@@ -616,7 +625,7 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   p.tiles_m = static_cast<int>(ceil_div(p.M, Cfg::kTileRows));
   p.tiles_n = static_cast<int>(ceil_div(p.N, TILE_N));
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kNumThreads);
+  cfg.blockDim = dim3(num_threads(FUSED, TILE_N));
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -820,7 +829,7 @@ extern "C" int ck_debug_resident_pairs(void) {
   auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16, false>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -1;
   cfg.gridDim = dim3(ck::sm_count() / 2 * 2);
-  cfg.blockDim = dim3(ck::kNumThreads);
+  cfg.blockDim = dim3(ck::num_threads(false, 256));
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
