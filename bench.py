@@ -199,11 +199,20 @@ class Workload:
         self.qx8 = [torch.empty(rows, K, **u8) for _ in range(ring)]
         self.bsx8 = [torch.empty(rp, K // 32, **u8) for _ in range(ring)]
         self.out = [torch.empty(rows, N, dtype=torch.bfloat16, device=device) for _ in range(ring)]
+        self.dyn_scale = torch.empty((), dtype=torch.float32, device=device)
+        self.scale_scratch = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
 
     def ring_bytes(self) -> int:
         per = self.x[0].numel() * 2 + self.qw[0].numel() + self.bsw[0].numel() + self.out[0].numel() * 2 + \
             self.qx[0].numel() + self.bsx[0].numel()
         return per * self.ring
+
+
+def _tensor_scale(lib, wl, i, st):
+    j = i % wl.ring
+    rc = lib.ck_nvfp4_tensor_scale(wl.x[j].data_ptr(), 2, wl.rows * K, wl.dyn_scale.data_ptr(), wl.scale_scratch.data_ptr(),
+                                   wl.scale_scratch.numel(), st)
+    assert rc == 0, lib.ck_last_error()
 
 
 def make_steps(lib, wl: Workload, case: str):
@@ -239,6 +248,7 @@ def make_steps(lib, wl: Workload, case: str):
     table = {
         "linear": (lambda i, st: (q4(i, st), g4(i, st)), 2, flops, None),
         "linear_mxfp8": (lambda i, st: (q8(i, st), g8(i, st)), 2, flops, None),
+        "tensor_scale": (lambda i, st: _tensor_scale(lib, wl, i, st), 1, None, 2 * rows * K + 4),
         "quantize_nvfp4": (q4, 1, None, q4_bytes),
         "quantize_mxfp8": (q8, 1, None, q8_bytes),
         "gemm_nvfp4": (g4, 1, flops, None),
@@ -606,7 +616,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="linear",
-                    choices=["linear", "linear_mxfp8", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
+                    choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
                              "sharded_gemm", "mlp_pair"])
     ap.add_argument("--shape", default="16384,15360,3072", help="M,N,K of --case sharded_gemm")
     ap.add_argument("--rows", type=int, default=0, help="override M (profiling of one kernel on a different size)")

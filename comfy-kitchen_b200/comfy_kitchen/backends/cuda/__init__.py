@@ -25,6 +25,7 @@ __all__ = [
     "scaled_mm_nvfp4",
     "scaled_mm_mxfp8",
     "linear_nvfp4_fused",
+    "nvfp4_tensor_scale",
 ]
 
 _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
@@ -49,12 +50,14 @@ _SIGNATURES = {
     "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_gemm_status": [_P],
+    "ck_nvfp4_tensor_scale_scratch_bytes": [_L],
+    "ck_nvfp4_tensor_scale": [_P, _I, _L, _P, _P, _L, _P],
     "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
     "ck_debug_resident_pairs": [],
     "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],
     "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
 }
-_RESTYPE = {"ck_last_error": ctypes.c_char_p}
+_RESTYPE = {"ck_last_error": ctypes.c_char_p, "ck_nvfp4_tensor_scale_scratch_bytes": ctypes.c_int64}
 
 
 def library_path() -> str:
@@ -160,6 +163,34 @@ def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor
         _check(lib.ck_quantize_mxfp8(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(qx), _ptr(sx), rows, cols, out_rows,
                                      out_cols, _stream(x.device)), "quantize_mxfp8")
     return qx.view(torch.float8_e4m3fn), sx.view(torch.float8_e8m0fnu)
+
+
+_scale_scratch: dict = {}
+
+
+def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
+    """0-d float32 tensor ``amax(|x|) / (448 * 6)`` (division in x's dtype), computed by one kernel.
+
+    The value the NVFP4 layout derives for a dynamically scaled tensor
+    (comfy_kitchen/tensor/nvfp4.py:64-69 of the reference).  The kernel's scratch buffer is
+    cached per (device, stream) and zeroed once when it is created.
+    """
+    lib = load_library()
+    x = _plain(x)
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    n = x.numel()
+    stream = _stream(x.device)
+    need = lib.ck_nvfp4_tensor_scale_scratch_bytes(n)
+    key = (x.device, stream)
+    scratch = _scale_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=x.device)
+        _scale_scratch[key] = scratch
+    out = torch.empty((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.ck_nvfp4_tensor_scale(_ptr(x), DTYPE_TO_CODE[x.dtype], n, _ptr(out), _ptr(scratch), scratch.numel(),
+                                         stream), "nvfp4_tensor_scale")
+    return out
 
 
 def dequantize_nvfp4(qx: torch.Tensor, per_tensor_scale: torch.Tensor, block_scales: torch.Tensor,

@@ -47,7 +47,12 @@ class TensorCoreNVFP4Layout(QuantizedLayout):
             raise ValueError(f"NVFP4 requires 2D tensor, got {tensor.dim()}D")
         orig_shape = tuple(tensor.shape)
         if scale is None or (isinstance(scale, str) and scale == "recalculate"):
-            scale = torch.amax(tensor.abs()) / (F8_E4M3_MAX * F4_E2M1_MAX)
+            if tensor.is_cuda and tensor.is_contiguous() and tensor.dtype in (torch.bfloat16, torch.float16, torch.float32):
+                from comfy_kitchen.backends import cuda as _cuda
+
+                scale = _cuda.nvfp4_tensor_scale(tensor)  # one kernel for abs, amax and the division
+            else:
+                scale = torch.amax(tensor.abs()) / (F8_E4M3_MAX * F4_E2M1_MAX)
         if not isinstance(scale, torch.Tensor):
             scale = torch.tensor(scale)
         scale = scale.to(device=tensor.device, dtype=torch.float32)

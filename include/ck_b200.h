@@ -102,6 +102,20 @@ CK_API int ck_quantize_mxfp8(const void* input, int input_dtype,
                       void* stream);
 
 /*
+ * Dynamic NVFP4 per-tensor scale: *scale_out = float32(dtype(amax(|input|)) / 2688) with the
+ * division carried out in the input dtype, i.e. the expression
+ * `torch.amax(x.abs()) / (448 * 6)` followed by `.to(float32)` of
+ * comfy_kitchen/tensor/nvfp4.py:64-69, in one kernel instead of three.
+ * `scratch` is device memory of at least ck_nvfp4_tensor_scale_scratch_bytes(num_elements)
+ * bytes that must be zero before the FIRST call; every call leaves it zeroed again, so one
+ * buffer can serve all calls that do not overlap on the GPU (calls that run concurrently
+ * need separate buffers).
+ */
+CK_API int64_t ck_nvfp4_tensor_scale_scratch_bytes(int64_t num_elements);
+CK_API int ck_nvfp4_tensor_scale(const void* input, int input_dtype, int64_t num_elements, float* scale_out,
+                          void* scratch, int64_t scratch_bytes, void* stream);
+
+/*
  * NVFP4 dequantization: packed codes uint8 [rows, cols/2] + swizzled E4M3 block
  * scales + one fp32 tensor scale -> [rows, cols] of out_dtype (f32/f16/bf16).
  * The arithmetic is done in the output dtype exactly as

@@ -169,3 +169,40 @@ def test_rejects_bad_inputs(ck, cuda_device):
         ck.quantize_nvfp4(torch.zeros(16, 24, dtype=torch.bfloat16, device=cuda_device), torch.ones((), device=cuda_device))
     with pytest.raises(AssertionError):
         ck.quantize_mxfp8(torch.zeros(32, 48, dtype=torch.bfloat16, device=cuda_device))
+
+
+# ------------------------------------------------------------------------------------------ dynamic tensor scale
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(1, 1), (16, 16), (33, 65), (256, 3072), (4096, 3072), (1000, 8193)])
+def test_dynamic_tensor_scale_matches_layout_expression(ck, cuda_device, dtype, shape):
+    """amax(|x|) / (448*6) in x's dtype, then float32 (reference tensor/nvfp4.py:64-69), evaluated on the CPU."""
+    from comfy_kitchen.backends import cuda as backend
+
+    g = torch.Generator(device="cpu").manual_seed(shape[0] + shape[1])
+    x = (torch.randn(*shape, generator=g) * 3).to(dtype)
+    want = (torch.amax(x.abs()) / (448.0 * 6.0)).to(torch.float32)
+    xd = x.to(cuda_device)
+    for _ in range(3):  # the scratch buffer is left clean by every call
+        got = backend.nvfp4_tensor_scale(xd)
+        assert got.dtype == torch.float32 and got.dim() == 0
+        assert got.cpu().view(torch.int32).item() == want.view(torch.int32).item()
+    # a tensor whose maximum sits in the very last element, and an unaligned view
+    y = torch.zeros(shape, dtype=dtype)
+    y.view(-1)[-1] = -7.0
+    assert backend.nvfp4_tensor_scale(y.to(cuda_device)).item() == (torch.amax(y.abs()) / 2688.0).float().item()
+    if x.numel() > 3:
+        sl = xd.view(-1)[1:]  # 2- or 4-byte aligned only
+        want_sl = (torch.amax(x.view(-1)[1:].abs()) / 2688.0).to(torch.float32)
+        assert backend.nvfp4_tensor_scale(sl).cpu().view(torch.int32).item() == want_sl.view(torch.int32).item()
+
+
+def test_layout_uses_the_dynamic_scale_kernel(ck, cuda_device):
+    from comfy_kitchen.tensor import QuantizedTensor
+
+    x = dit_activation(512, 1024).to(cuda_device)
+    qt = QuantizedTensor.from_float(x, "TensorCoreNVFP4Layout")
+    want = layout_scale(x.cpu())
+    assert qt.params.scale.cpu().view(torch.int32).item() == want.view(torch.int32).item()
+    rq, rs = oc.quantize_nvfp4(as_f32(x), np.float32(want.item()))
+    np.testing.assert_array_equal(bits(qt._qdata), rq)
+    np.testing.assert_array_equal(bits(qt.params.block_scale), rs)
