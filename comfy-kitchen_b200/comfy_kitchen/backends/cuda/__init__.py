@@ -52,6 +52,7 @@ _SIGNATURES = {
     "ck_gemm_status": [_P],
     "ck_nvfp4_tensor_scale_scratch_bytes": [_L],
     "ck_nvfp4_tensor_scale": [_P, _I, _L, _P, _P, _L, _P],
+    "ck_nvfp4_tensor_scale_noalloc": [_P, _I, _L, _P, _P],
     "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
     "ck_debug_resident_pairs": [],
     "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],

@@ -10,6 +10,7 @@
 // words 64.. = one float per block (the gap keeps the counter on its own 256-byte line).
 #include "ck_common.cuh"
 
+#include <mutex>
 #include <type_traits>
 
 namespace ck {
@@ -143,8 +144,58 @@ int run(const char* op, const void* x, int dtype, int64_t n, float* scale_out, u
   return CK_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Variant with built-in scratch, for callers that must not allocate.
+// ---------------------------------------------------------------------------
+// The partial maxima and the ticket counter live in this fixed device array instead of a
+// caller-supplied buffer.  It exists once per GPU that loads the library and stays
+// resident until the process exits.  In host code the name below is only a handle, not a
+// device address; the address is looked up once per device (static_scratch_for_device).
+constexpr int64_t kStaticMaxBlocks = 16384;                          // 64 KiB of partials
+constexpr int64_t kStaticMaxElements = kStaticMaxBlocks * kChunk;    // 134 217 728 elements
+static __device__ __align__(256) unsigned int g_static_scratch[kPartialOffset + kStaticMaxBlocks];
+
+// Device address of g_static_scratch on the current device.  The first call on a device
+// performs the lookup (which may make the runtime load this module), later calls reuse it.
+int static_scratch_for_device(unsigned int** out) {
+  static std::mutex mu;
+  static unsigned int* per_device[64] = {nullptr};
+  int dev = 0;
+  CK_CUDA(cudaGetDevice(&dev));
+  CK_REQUIRE(dev >= 0 && dev < 64, "nvfp4_tensor_scale_noalloc: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (per_device[dev] == nullptr) {
+    unsigned int* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      return fail(CK_ERR_CUDA, "cudaGetSymbolAddress(g_static_scratch) failed on device %d: %s", dev,
+                  cudaGetErrorString(e));
+    }
+    per_device[dev] = ptr;
+  }
+  *out = per_device[dev];
+  return CK_OK;
+}
+
 }  // namespace
 }  // namespace ck
+
+extern "C" int ck_nvfp4_tensor_scale_noalloc(const void* input, int input_dtype, int64_t num_elements,
+                                             float* scale_out, void* stream) {
+  using namespace ck;
+  CK_REQUIRE(num_elements <= kStaticMaxElements,
+             "nvfp4_tensor_scale_noalloc: %lld elements exceed the built-in scratch (at most %lld elements); use "
+             "ck_nvfp4_tensor_scale with your own scratch buffer",
+             (long long)num_elements, (long long)kStaticMaxElements);
+  unsigned int* scratch = nullptr;
+  if (int rc = static_scratch_for_device(&scratch)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  Only the ticket counter has to start
+  // at zero (every partial that is read is written first); clear it in stream order.
+  CK_CUDA(cudaMemsetAsync(scratch, 0, sizeof(unsigned int), s));
+  return run("nvfp4_tensor_scale_noalloc", input, input_dtype, num_elements, scale_out, scratch,
+             static_cast<int64_t>(sizeof(unsigned int)) * (kPartialOffset + kStaticMaxBlocks), s);
+}
 
 extern "C" int64_t ck_nvfp4_tensor_scale_scratch_bytes(int64_t num_elements) {
   if (num_elements <= 0) return 0;

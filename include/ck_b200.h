@@ -116,6 +116,25 @@ CK_API int ck_nvfp4_tensor_scale(const void* input, int input_dtype, int64_t num
                           void* scratch, int64_t scratch_bytes, void* stream);
 
 /*
+ * Same result as ck_nvfp4_tensor_scale, for callers that cannot hand in a scratch buffer
+ * because they must not allocate device memory at that point: code running between
+ * cudaStreamBeginCapture and EndCapture, plugins that live inside a host application with
+ * a fixed memory budget, or serving loops where a cudaMalloc would stall every stream of
+ * the device.  This entry point has no counterpart in the reference.  It allocates
+ * nothing: its scratch is a fixed array inside the library (about 64 KiB per GPU, resident
+ * from the moment the library is loaded on that GPU until the process exits).
+ *   - Limit: num_elements <= 134 217 728 (16384 blocks of 8192 elements); larger inputs
+ *     are refused with CK_ERR_INVALID_ARGUMENT - use ck_nvfp4_tensor_scale instead.
+ *   - The first call on each device looks up the array's device address (one-off set-up
+ *     that may make the CUDA runtime load the library's kernels); make that first call
+ *     before any stream capture starts.
+ *   - All calls on one device share the array: two calls whose kernels can overlap on the
+ *     GPU (different streams without an ordering between them) race and return garbage.
+ */
+CK_API int ck_nvfp4_tensor_scale_noalloc(const void* input, int input_dtype, int64_t num_elements,
+                                  float* scale_out, void* stream);
+
+/*
  * NVFP4 dequantization: packed codes uint8 [rows, cols/2] + swizzled E4M3 block
  * scales + one fp32 tensor scale -> [rows, cols] of out_dtype (f32/f16/bf16).
  * The arithmetic is done in the output dtype exactly as
