@@ -117,10 +117,9 @@ CK_API int ck_nvfp4_tensor_scale(const void* input, int input_dtype, int64_t num
 
 /*
  * Same result as ck_nvfp4_tensor_scale, for callers that cannot hand in a scratch buffer
- * because they must not allocate device memory at that point: code running between
- * cudaStreamBeginCapture and EndCapture, plugins that live inside a host application with
- * a fixed memory budget, or serving loops where a cudaMalloc would stall every stream of
- * the device.  This entry point has no counterpart in the reference.  It allocates
+ * because they must not allocate device memory at that point: plugins that live inside a
+ * host application with a fixed memory budget, or serving loops where a cudaMalloc would
+ * stall every stream of the device.  This entry point has no counterpart in the reference.  It allocates
  * nothing: its scratch is a fixed array inside the library (about 64 KiB per GPU, resident
  * from the moment the library is loaded on that GPU until the process exits).
  *   - Limit: num_elements <= 134 217 728 (16384 blocks of 8192 elements); larger inputs
