@@ -45,15 +45,25 @@ constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
 // Epilogue warps per CTA: two per 32-lane quarter of tensor memory for the plain epilogue,
 // four for the fused one (its activation + quantization arithmetic is ~30 instructions per
 // element and must keep up with the tensor pipe).
-constexpr int epilogue_warps(bool fused, int tile_n) { return (fused && tile_n >= 256) ? 16 : 8; }
-constexpr int num_threads(bool fused, int tile_n) { return 64 + 32 * epilogue_warps(fused, tile_n); }  // + TMA, MMA warps
+// A CTA pair with 192-wide tiles uses three (64 columns each, whole 128-byte store boxes).
+constexpr int epilogue_warps(bool fused, int tile_n, int ctas) {
+  return (fused && tile_n >= 256) ? 16 : (ctas == 2 && tile_n == 192) ? 12 : 8;
+}
+constexpr int num_threads(bool fused, int tile_n, int ctas) {
+  return 64 + 32 * epilogue_warps(fused, tile_n, ctas);  // + TMA, MMA warps
+}
 constexpr int kTmemCols = 512;
 
 // CTAS == 2: a pair of CTAs (a 2-CTA cluster on neighbouring SMs) computes one 256 x TILE_N
 // tile with cta_group::2 instructions.  Each CTA loads its own 128 rows of A and only its
 // own half of B's rows, which halves the shared-memory traffic for B - the limiter of the
 // single-CTA FP4 kernel.
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS>
+// OUT_STAGE: the plain epilogue stages the converted tile in shared memory (4 KiB per
+// epilogue warp) and writes it with TMA stores.  Storing rows straight from registers puts 32
+// partial-line writes per instruction into the SM's memory pipeline, which delays the MMA
+// warp's own instructions in that pipeline and starves the tensor cores.
+// (OUT_STAGE = number of 4 KiB boxes per epilogue warp, used as a ring; 0 = store from registers.)
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, int OUT_STAGE = 0>
 struct Config {
   static constexpr int kTileRows = kTileM * CTAS;      // rows of the output tile
   static constexpr int kBRows = TILE_N / CTAS;         // rows of B each CTA loads
@@ -68,8 +78,10 @@ struct Config {
   static constexpr int kSfaBytes = kSfTilesPerStage * 512;
   static constexpr int kSfbBytes = kSfbRowBlocks * kSfTilesPerStage * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBytes =
-      STAGES * kStageBytes + 2 * TILE_N * 4 /*bias*/ + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kOutStageBytes = OUT_STAGE * epilogue_warps(false, TILE_N, CTAS) * 4096;
+  static constexpr int kRingBytes = (STAGES * kStageBytes + 1023) / 1024 * 1024;
+  static constexpr int kSmemBytes = kRingBytes + kOutStageBytes + 2 * TILE_N * 4 /*bias*/ +
+                                    1024 /*alignment slack*/ + 256 /*barriers*/;
   // tensor memory columns
   static constexpr int kAccCols = TILE_N;
   static constexpr int kSfaCol = NUM_ACC * kAccCols;
@@ -107,6 +119,7 @@ struct GemmParams {
   int n_row_blocks_a;      // ceil(M / 128)
   int n_row_blocks_b;      // ceil(N / 128)
   int tiles_m, tiles_n;
+  int out_tma;             // the output qualifies for TMA stores (16-byte aligned base and pitch)
   int* status;             // device status word: set non-zero when a wait gave up
   // fused epilogue (FUSED kernels only)
   int activation;          // CK_ACT_*
@@ -116,6 +129,38 @@ struct GemmParams {
 };
 
 __device__ int g_gemm_status = 0;
+
+// Optional per-tile timeline (SM cycle counter) for tuning; compiled in with -DCK_GEMM_TRACE only.
+#ifdef CK_GEMM_TRACE
+constexpr int kTraceTiles = 40;
+constexpr int kTraceSlots = 16;
+__device__ long long g_trace[160 * kTraceTiles * kTraceSlots];
+__device__ long long g_trace2[160 * 4 * 64];
+#define CK_TRACE2(kind, idx)                                                                         \
+  do {                                                                                               \
+    if (lane == 0 && (idx) < 64 && blockIdx.x < 160) g_trace2[(blockIdx.x * 4 + (kind)) * 64 + (idx)] = clock64(); \
+  } while (0)
+#define CK_TRACE(slot)                                                                               \
+  do {                                                                                               \
+    if (lane == 0 && tile_it < kTraceTiles && blockIdx.x < 160)                                      \
+      g_trace[(blockIdx.x * kTraceTiles + tile_it) * kTraceSlots + (slot)] = clock64();             \
+  } while (0)
+#define CK_TRACE_ELECTED(slot)                                                                       \
+  do {                                                                                               \
+    if (tile_it < kTraceTiles && blockIdx.x < 160)                                                   \
+      g_trace[(blockIdx.x * kTraceTiles + tile_it) * kTraceSlots + (slot)] = clock64();             \
+  } while (0)
+#else
+#define CK_TRACE(slot) \
+  do {                 \
+  } while (0)
+#define CK_TRACE2(kind, idx) \
+  do {                       \
+  } while (0)
+#define CK_TRACE_ELECTED(slot) \
+  do {                         \
+  } while (0)
+#endif
 
 // alpha * acc + bias for 32 consecutive output columns of one row.  `bias_s` points at the 32
 // fp32 bias values of these columns in shared memory (all lanes read the same addresses).
@@ -208,13 +253,14 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
 // FUSED: the epilogue applies an activation to the output rounded to OutT (what an unfused
 // caller would see), optionally stores it, and optionally re-quantizes it to NVFP4 (codes +
 // tiled block scales against a static per-tensor scale) as the A operand of the next GEMM.
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED>
-__global__ void __launch_bounds__(num_threads(FUSED, TILE_N), 1)
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED, int OUT_STAGE>
+__global__ void __launch_bounds__(num_threads(FUSED, TILE_N, CTAS), 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                         const GemmParams p) {
-  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
-  constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N);
+                         const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OUT_STAGE>;
+  static_assert(!(FUSED && OUT_STAGE != 0), "the fused epilogue stores from registers");
+  constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N, CTAS);
   // In a CTA pair, rank 0 (the leader) issues the MMAs for both CTAs.
   const uint32_t cta_rank = (CTAS == 2) ? cluster_cta_rank() : 0u;
   const int worker = blockIdx.x / CTAS;        // index of this CTA (pair) among the tile workers
@@ -226,7 +272,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem_b = smem_a + STAGES * Cfg::kABytes;
   uint8_t* smem_sfa = smem_b + STAGES * Cfg::kBBytes;
   uint8_t* smem_sfb = smem_sfa + STAGES * Cfg::kSfaBytes;
-  float* smem_bias = reinterpret_cast<float*>(smem_sfb + STAGES * Cfg::kSfbBytes);  // [2][TILE_N]
+  uint8_t* smem_out = smem + Cfg::kRingBytes;  // 1024-byte aligned (swizzled store boxes)
+  float* smem_bias = reinterpret_cast<float*>(smem_out + Cfg::kOutStageBytes);  // [2][TILE_N]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bias + 2 * TILE_N);
   uint64_t* full_bar = bars;                       // [STAGES] producer -> MMA
   uint64_t* empty_bar = bars + STAGES;             // [STAGES] MMA -> producer
@@ -251,6 +298,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
+    if constexpr (OUT_STAGE != 0) prefetch_tensormap(&map_out);
   }
   if (warp == 1) tmem_alloc<CTAS>(tmem_base_slot, kTmemCols);
   tc_fence_before_sync();
@@ -268,7 +316,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
-    for (int tile = worker; tile < num_tiles; tile += num_workers) {
+    [[maybe_unused]] uint32_t tile_it = 0;
+    for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
       // consecutive workers take tiles that share the B columns (tile_m fastest)
       const int tile_m = tile % p.tiles_m;
       const int tile_n = tile / p.tiles_m;
@@ -290,6 +339,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         } else {
           mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
         }
+        if (ks == 0) CK_TRACE(4);
+        if (ks == k_stages - 1) CK_TRACE(5);
+        CK_TRACE2(0, it);
         if constexpr (CTAS == 2) {
           // Every load of both CTAs reports its bytes to the leader's barrier; scale tiles
           // come through 3-D tensor maps {512 B, column tile, row block} so that tiles past
@@ -355,23 +407,25 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int n0 = (tile / p.tiles_m) * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
-      if constexpr (CTAS == 2) {
-        mbar_wait_cluster(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
-      } else {
-        mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
-      }
-      tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
       // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
       const uint32_t sfb_shift = (n0 % 128) / 32;
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
+        CK_TRACE2(1, it);
         if constexpr (CTAS == 2) {
           mbar_wait_cluster(&full_bar[s], ph, abort_flag);
         } else {
           mbar_wait(&full_bar[s], ph, abort_flag);
         }
+        if (ks == 0) CK_TRACE(2);
+        if (ks == k_stages - 1) CK_TRACE(3);
+        CK_TRACE2(2, it);
+#ifdef CK_GEMM_TRACE
+        if (tile_it == 1 && ks < kTraceSlots && lane == 0 && blockIdx.x < 160)
+          g_trace[(blockIdx.x * kTraceTiles + kTraceTiles - 1) * kTraceSlots + ks] = clock64();
+#endif
         tc_fence_after_sync();
         if (elect_one()) {
           const uint32_t a_lo = a_lo0 + s * (Cfg::kABytes >> 4);
@@ -393,6 +447,15 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                            desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
             }
           }
+          if (ks == 0) {
+            // Only now does the tile need its accumulator: the wait for the epilogue to have
+            // drained it comes after the first stage's operands have landed and its scale
+            // copies are issued, which takes those steps off the tile-to-tile critical path.
+            CK_TRACE_ELECTED(0);
+            mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
+            CK_TRACE_ELECTED(1);
+            tc_fence_after_sync();
+          }
 #pragma unroll
           for (int kb = 0; kb < kMmaPerStage; ++kb) {
             if (kb < n_mma) {
@@ -411,6 +474,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
           }
           // stage reusable once these MMAs and copies retire; in a pair both CTAs are told
+#ifdef CK_GEMM_TRACE
+          if (tile_it == 1 && ks < kTraceSlots && blockIdx.x < 160)
+            g_trace[(blockIdx.x * kTraceTiles + kTraceTiles - 2) * kTraceSlots + ks] = clock64();
+#endif
           tc_commit<CTAS>(empty_addr + s * 8);
           if constexpr (CTAS == 2) tc_commit<CTAS>(empty_addr_peer + s * 8);
           if (ks == k_stages - 1) {
@@ -419,6 +486,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
         }
         __syncwarp();
+        CK_TRACE2(3, it);
       }
     }
   } else {
@@ -443,6 +511,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const bool vec_ok = (static_cast<int64_t>(p.N) * sizeof(OutT)) % 32 == 0 &&
                         (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (TILE_N * sizeof(OutT)) % 32 == 0;
     const uint32_t acc_empty_leader = (CTAS == 2) ? map_to_cta(smem_u32(acc_empty_bar), 0) : 0u;
+    [[maybe_unused]] uint32_t out_box = 0;  // boxes this warp has staged so far (ring index)
     uint32_t tile_it = 0;
     for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
       const int tile_m = tile % p.tiles_m;
@@ -458,11 +527,13 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         bias_s[c] = (p.bias != nullptr && n < p.N) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
+      if (warp == 2) CK_TRACE(6);
       if constexpr (CTAS == 2) {
         mbar_wait_cluster(&acc_full_bar[acc], acc_ph, abort_flag);
       } else {
         mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);
       }
+      if (warp == 2) CK_TRACE(7);
       tc_fence_after_sync();
       const int c0 = half * kColsPerWarp;
       const uint32_t t_row = tmem_base + acc * Cfg::kAccCols + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
@@ -470,6 +541,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) tmem_load_32x32(t_row + c * 32, buf[c]);
       tmem_load_wait();
+      if (warp == 2) CK_TRACE(8);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -481,13 +553,79 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0 + c0;
       if constexpr (!FUSED) {
+        bool staged = false;
+        if constexpr (OUT_STAGE != 0) staged = p.out_tma != 0;
+        if (staged) {
+          if constexpr (OUT_STAGE != 0) {
+            // The warp's 32 rows x 128 bytes of converted output go to its staging box in the
+            // 128-byte-swizzled layout (16-byte unit j of row r at r*128 + ((j ^ r%8) * 16):
+            // conflict-free for the 8 lanes of a store phase), then one TMA store writes whole
+            // lines; rows past M and columns past N are clipped by the tensor map.
+            constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));
+            constexpr int kChunksPerBox = kBoxCols / 32;          // 2 for 16-bit outputs, 1 for fp32
+            constexpr int kUnitsPerChunk = 32 * static_cast<int>(sizeof(OutT)) / 16;
+            const uint32_t stage_warp = smem_u32(smem_out) + (warp - 2) * (OUT_STAGE * 4096);
+            const int row0 = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM + quarter * 32;
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const int valid = min(32, p.N - (n0 + c0 + c * 32));
-          if (row < p.M && valid > 0) {
-            float v[32];
-            scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
-            store_row_chunk<OutT>(out_row + c * 32, v, valid, vec_ok);
+            for (int c = 0; c < kChunks; ++c) {
+              const uint32_t stage_box = stage_warp + (out_box % OUT_STAGE) * 4096;
+              const uint32_t stage_row = stage_box + lane * 128;
+              if (c % kChunksPerBox == 0) {
+                if (lane == 0) bulk_wait_group_read<OUT_STAGE - 1>();  // the store that last used this box has read it
+                __syncwarp();
+              }
+              float v[32];
+              scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
+#pragma unroll
+              for (int u = 0; u < kUnitsPerChunk; ++u) {
+                uint32_t w[4];
+                if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+                      __nv_bfloat162 q = __floats2bfloat162_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
+                      w[j] = *reinterpret_cast<uint32_t*>(&q);
+                    } else {
+                      __half2 q = __floats2half2_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
+                      w[j] = *reinterpret_cast<uint32_t*>(&q);
+                    }
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(v[u * 4 + j]);
+                }
+                const int unit = (c % kChunksPerBox) * kUnitsPerChunk + u;
+#ifdef CK_EXP_NOSTS
+                if (w[0] == 0x12345678u && w[3] == 0x9abcdef0u)
+#endif
+                st_shared_128(stage_row + (((unit ^ lane) & 7) << 4), w[0], w[1], w[2], w[3]);
+              }
+              if (c % kChunksPerBox == kChunksPerBox - 1) {
+                fence_proxy_async();  // the staged bytes become visible to the TMA engine
+                __syncwarp();
+                const int col = n0 + c0 + (c / kChunksPerBox) * kBoxCols;
+#ifdef CK_EXP_NOTMASTORE
+                if (lane == 0 && row0 < p.M && col < p.N && alpha == 123.456f) {
+#else
+                if (lane == 0 && row0 < p.M && col < p.N) {
+#endif
+                  tma_store_2d_addr(&map_out, stage_box, col, row0);
+                }
+                // (an empty group when nothing was stored keeps the ring's group count in step)
+                if (lane == 0) bulk_commit_group();
+                ++out_box;
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            const int valid = min(32, p.N - (n0 + c0 + c * 32));
+            if (row < p.M && valid > 0) {
+              float v[32];
+              scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
+              store_row_chunk<OutT>(out_row + c * 32, v, valid, vec_ok);
+            }
           }
         }
       } else {
@@ -539,6 +677,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
         }
       }
+      if (warp == 2) CK_TRACE(9);
+    }
+    if constexpr (OUT_STAGE != 0) {
+      if (lane == 0) bulk_wait_group_read0();  // shared memory stays valid until the last store has read it
     }
   }
 
@@ -610,10 +752,26 @@ int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64
   return CK_OK;
 }
 
-template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED>
+// Row-major [rows, cols] output of `elem_bytes`-wide elements: boxes of 32 rows x 128 bytes,
+// 128-byte swizzle (the layout the epilogue stages its rows in).
+int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const CUtensorMapDataType type = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * elem_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), 32};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = fn(map, type, 2, base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", static_cast<int>(r));
+  return CK_OK;
+}
+
+template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED, int OUT_STAGE = 0>
 int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, cudaStream_t stream) {
-  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS>;
-  auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT, FUSED>;
+  using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OUT_STAGE>;
+  auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT, FUSED, OUT_STAGE>;
   // the dynamic shared-memory opt-in is per device: do it once for each device that launches
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -625,7 +783,7 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   p.tiles_m = static_cast<int>(ceil_div(p.M, Cfg::kTileRows));
   p.tiles_n = static_cast<int>(ceil_div(p.N, TILE_N));
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(num_threads(FUSED, TILE_N));
+  cfg.blockDim = dim3(num_threads(FUSED, TILE_N, CTAS));
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -649,14 +807,27 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
     }
     if (dev >= 0 && dev < 64) max_workers[dev].store(resident, std::memory_order_release);
   }
-  const int workers = min(p.tiles_m * p.tiles_n, resident);
+  int workers = min(p.tiles_m * p.tiles_n, resident);
+#ifdef CK_GEMM_TRACE
+  if (const char* e = getenv("CK_GEMM_MAX_WORKERS")) workers = min(workers, atoi(e));
+#endif
   cfg.gridDim = dim3(workers * CTAS);
   CUtensorMap map_sfa = {}, map_sfb = {};
   if (CTAS == 2) {
     if (int rc = make_scale_map(&map_sfa, p.sfa, p.n_row_blocks_a, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
     if (int rc = make_scale_map(&map_sfb, p.sfb, p.n_row_blocks_b, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
   }
-  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, p));
+  CUtensorMap map_out = {};
+  p.out_tma = 0;
+  if constexpr (OUT_STAGE != 0) {
+    // TMA stores need a 16-byte aligned base and row pitch; other outputs take the register path
+    if (p.out != nullptr && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 &&
+        (static_cast<int64_t>(p.N) * sizeof(OutT)) % 16 == 0) {
+      if (int rc = make_output_map(&map_out, p.out, p.M, p.N, sizeof(OutT))) return rc;
+      p.out_tma = 1;
+    }
+  }
+  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, map_out, p));
   return CK_OK;
 }
 
@@ -664,14 +835,15 @@ int forced_config() {
   // CK_GEMM_CONFIG pins the kernel configuration (tuning aid); unset = choose by shape.
   //   1 = one CTA, 128 x 128 tiles      2 = one CTA, 128 x 192 tiles (two accumulators)
   //   3 = one CTA, 128 x 256 tiles      4 = CTA pair, 256 x 256 tiles
+  //   5 = CTA pair, 256 x 192 tiles (two accumulators)
   const char* e = getenv("CK_GEMM_CONFIG");
   return e ? atoi(e) : 0;
 }
 
 template <Kind KIND, typename OutT, bool FUSED>
-int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[3], const GemmParams& p,
+int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[4], const GemmParams& p,
                      cudaStream_t stream) {
-  // map_b[0|1|2] have boxes of 128 | 192 | 256 rows.
+  // map_b[0|1|2|3] have boxes of 128 | 192 | 256 | 96 rows.
   int config = forced_config();
   if (config == 0) {
     const int64_t pair_tiles = ceil_div(p.M, 256) * ceil_div(p.N, 256);
@@ -685,14 +857,21 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[3], co
     }
   }
   switch (config) {
+    case 6:
+      if constexpr (!FUSED) return launch_config<KIND, 256, 1, 4, 2, OutT, false, 2>(map_a, map_b[0], p, stream);
+      [[fallthrough]];
+    case 5:
+      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 5, 2, OutT, false, 1>(map_a, map_b[3], p, stream);
+      [[fallthrough]];
     case 4:
-      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED>(map_a, map_b[0], p, stream);
+      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED, FUSED ? 0 : 1>(map_a, map_b[0], p, stream);
     case 3:
       return launch_config<KIND, 256, 1, 4, 1, OutT, FUSED>(map_a, map_b[2], p, stream);
     case 2:
       if constexpr (!FUSED) return launch_config<KIND, 192, 2, 4, 1, OutT, false>(map_a, map_b[1], p, stream);
       [[fallthrough]];  // the fused epilogue needs 64-column warp shares: no 192-wide variant
     default:
+      if constexpr (!FUSED) return launch_config<KIND, 128, 2, 5, 1, OutT, false, 1>(map_a, map_b[0], p, stream);
       return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, stream);
   }
 }
@@ -760,11 +939,12 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
 
-  CUtensorMap map_a, map_b[3];
+  CUtensorMap map_a, map_b[4];
   if (int rc = make_operand_map(&map_a, a, M, p.k_bytes, kTileM)) return rc;
   if (int rc = make_operand_map(&map_b[0], b, N, p.k_bytes, 128)) return rc;
   if (int rc = make_operand_map(&map_b[1], b, N, p.k_bytes, 192)) return rc;
   if (int rc = make_operand_map(&map_b[2], b, N, p.k_bytes, 256)) return rc;
+  if (int rc = make_operand_map(&map_b[3], b, N, p.k_bytes, 96)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if constexpr (KIND == Kind::kNvfp4) {
     if (fused.enabled) {
@@ -825,11 +1005,11 @@ extern "C" int ck_linear_nvfp4_fused(const void* a, const void* b, const void* s
 // (diagnostic; 0 until that configuration has launched once).
 extern "C" int ck_debug_resident_pairs(void) {
   cudaLaunchConfig_t cfg = {};
-  using Cfg = ck::Config<ck::Kind::kNvfp4, 256, 1, 5, 2>;
-  auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16, false>;
+  using Cfg = ck::Config<ck::Kind::kNvfp4, 256, 1, 5, 2, 1>;
+  auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16, false, 1>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -1;
   cfg.gridDim = dim3(ck::sm_count() / 2 * 2);
-  cfg.blockDim = dim3(ck::num_threads(false, 256));
+  cfg.blockDim = dim3(ck::num_threads(false, 256, 2));
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -842,6 +1022,20 @@ extern "C" int ck_debug_resident_pairs(void) {
   if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) return -1;
   return clusters;
 }
+
+#ifdef CK_GEMM_TRACE
+// Copies the per-tile timeline to the host: [160 CTAs][40 tiles][16 slots] of SM cycle counts.
+extern "C" __attribute__((visibility("default"))) int ck_debug_trace(long long* host_out) {
+  CK_CUDA(cudaDeviceSynchronize());
+  CK_CUDA(cudaMemcpyFromSymbol(host_out, ck::g_trace, sizeof(long long) * 160 * ck::kTraceTiles * ck::kTraceSlots));
+  return CK_OK;
+}
+extern "C" __attribute__((visibility("default"))) int ck_debug_trace2(long long* host_out) {
+  CK_CUDA(cudaDeviceSynchronize());
+  CK_CUDA(cudaMemcpyFromSymbol(host_out, ck::g_trace2, sizeof(long long) * 160 * 4 * 64));
+  return CK_OK;
+}
+#endif
 
 // Device status word of the GEMM kernels: 0 = every wait completed; non-zero = some wait
 // gave up (results of that launch are invalid).  Synchronises the device; resets the word.

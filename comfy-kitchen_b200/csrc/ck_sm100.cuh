@@ -54,6 +54,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;  // common case: no shared-memory read of the flag
   if (*abort_flag) return false;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -84,33 +85,19 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// arrive on an mbarrier of another CTA of the cluster (address from map_to_cta)
+// Arrive on an mbarrier of another CTA of the cluster (address from map_to_cta).  The
+// barriers of the GEMM kernels order tensor-memory and asynchronous-proxy traffic only (the
+// tcgen05 fences and commits carry that ordering), never data written with ordinary stores,
+// so CTA-scope barrier semantics are enough for waits and arrivals that cross the pair; the
+// cluster-scope forms cost several hundred cycles per call.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-// Non-blocking poll with cluster-scope acquire (the arrival may come from the other CTA).
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// mbar_wait with cluster-scope acquire: for barriers another CTA of the pair arrives on
+// Wait on a barrier of this CTA that the other CTA of the pair (or a tcgen05.commit issued
+// there) arrives on.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (*abort_flag) return false;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
+  return mbar_wait(bar, parity, abort_flag);
 }
 
 // One lane of a converged warp (the same lane every time for a full warp).
@@ -167,6 +154,33 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
                    smem_u32(smem_dst)),
                "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
+}
+
+// 2-D tiled store shared memory -> global (bulk async group of the executing thread).  The
+// box is clipped at the tensor's bounds; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_addr(const CUtensorMap* map, uint32_t smem_addr, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_addr), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once the bulk stores committed by this thread have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... until at most kPending of them are still reading.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 // ---------------------------------------------------------------------------
