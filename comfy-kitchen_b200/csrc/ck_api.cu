@@ -1,6 +1,7 @@
 // Library-level entry points: version, error text, device probe.
 #include "ck_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace ck {
@@ -28,6 +29,14 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("CK_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
 }
 
 }  // namespace ck

@@ -36,6 +36,37 @@ __host__ __device__ constexpr int64_t ceil_div(int64_t x, int64_t m) { return (x
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// The streaming kernels and the GEMMs of this library are launched with programmatic stream
+// serialization: each kernel lets its successor start being scheduled at once
+// (pdl_launch_dependents at its top) and itself waits for its predecessor in the stream to
+// have completed and flushed (pdl_wait) before it touches global memory.  The successor's
+// launch latency and set-up then overlap the predecessor's tail instead of following it.
+// A kernel launched this way behind a kernel that never triggers simply starts when that one
+// ends; CK_PDL=0 turns the attribute off.
+bool pdl_enabled();
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ---- swizzled scale layout --------------------------------------------------
 // Byte offset of the scale of (row r, scale column c) in the 128x4-tiled
 // buffer: each tile of 128 rows x 4 columns is 512 contiguous bytes laid out

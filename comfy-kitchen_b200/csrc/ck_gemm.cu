@@ -306,6 +306,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if constexpr (CTAS == 2) cluster_sync_all();  // the other CTA's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Everything above is independent of the kernel before this one in the stream; operands,
+  // scales and the output buffer are not.
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int k_stages = (p.k_bytes + kStageKBytes - 1) / kStageKBytes;
@@ -786,13 +790,15 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   cfg.blockDim = dim3(num_threads(FUSED, TILE_N, CTAS));
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CTAS;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   // Persistent workers must all be resident at once.  For CTA pairs the number of
   // co-resident clusters can be below sm_count / 2 (pairs must sit in one GPC): ask.
   static std::atomic<int> max_workers[64];

@@ -6,6 +6,8 @@
 
 #include "ck_common.cuh"
 
+#include <type_traits>
+
 namespace ck {
 namespace quant {
 
@@ -109,6 +111,122 @@ __device__ __forceinline__ void nvfp4_block(const float (&v)[16], float g, bool 
   }
   lo_word = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
   hi_word = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4 block for the streaming quantizer: 16 elements of a 16-bit type as eight packed
+// words.  Same arithmetic as nvfp4_block, arranged for a low instruction count: packed
+// abs-max, the two per-block divisions (by 6, by the tensor scale) as reciprocal-FMA
+// quotients with reciprocals prepared once per thread, the zero-scale case resolved on the
+// packed words, four E2M1 converts packed per 32-bit word, and the nibble order a
+// template parameter.
+// ---------------------------------------------------------------------------
+
+// word = bytes {e2m1x2(f0,f1), e2m1x2(f2,f3), e2m1x2(f4,f5), e2m1x2(f6,f7)}, lowest byte first;
+// within a byte the first argument goes to the high nibble.
+__device__ __forceinline__ uint32_t f32x8_to_e2m1_word(float f0, float f1, float f2, float f3, float f4, float f5,
+                                                       float f6, float f7) {
+  uint32_t r;
+  asm("{ .reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %1, %2;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %3, %4;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %5, %6;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %7, %8;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3}; }"
+      : "=r"(r)
+      : "f"(f0), "f"(f1), "f"(f2), "f"(f3), "f"(f4), "f"(f5), "f"(f6), "f"(f7));
+  return r;
+}
+
+// a / b for a >= 0 (no sign to restore) with y = RN(1/b); see div_markstein.
+__device__ __forceinline__ float div_markstein_nonneg(float a, float b, float y) {
+  float q = __fmul_rn(a, y);
+  float r = __fmaf_rn(-b, q, a);
+  q = __fmaf_rn(r, y, q);
+  r = __fmaf_rn(-b, q, a);
+  return __fmaf_rn(r, y, q);
+}
+
+// max |.| over the 16 values packed in eight words, as a float
+template <typename T>
+__device__ __forceinline__ float amax16_packed(const uint32_t (&w)[8]) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i])));
+    const uint32_t b = *reinterpret_cast<uint32_t*>(&m);
+    return fmaxf(__uint_as_float(b << 16), __uint_as_float(b & 0xFFFF0000u));
+  } else {
+    __half2 m = __habs2(*reinterpret_cast<const __half2*>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __half2*>(&w[i])));
+    const float2 f = __half22float2(m);
+    return fmaxf(f.x, f.y);
+  }
+}
+
+// Per-thread constants of the tensor scale g: its reciprocal and whether g lies in the
+// range where the reciprocal-FMA quotients below are exact.
+struct TensorScale {
+  float g, rcp;
+  bool in_window;
+};
+__device__ __forceinline__ TensorScale make_tensor_scale(float g) {
+  TensorScale t;
+  t.g = g;
+  t.in_window = (g >= 0x1p-40f) && (g <= 0x1p40f);
+  t.rcp = __frcp_rn(t.in_window ? g : 1.0f);
+  return t;
+}
+
+template <typename T, bool kHiFirst>
+__device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const TensorScale& ts, uint32_t& lo_word,
+                                                   uint32_t& hi_word, uint32_t& scale_byte) {
+  static_assert(sizeof(T) == 2, "packed 16-bit inputs");
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  const float amax = amax16_packed<T>(w);
+  // Exactness window of the reciprocal-FMA quotients (all residuals representable): tensor
+  // scale within 2^+-40, amax zero or within 2^+-60; then amax/6/g and every x/total below
+  // are normal numbers with normal residuals.  Anything else takes the IEEE-division path.
+  const bool fast_s = ts.in_window && (amax <= 0x1p60f) && (amax >= 0x1p-60f || amax == 0.0f);
+  if (fast_s) {
+    float s = div_markstein_nonneg(div_markstein_nonneg(amax, 6.0f, 0x1.555556p-3f /* RN(1/6) */), ts.g, ts.rcp);
+    s = fminf(s, 448.0f);
+    scale_byte = f32_to_e4m3_byte(s);
+    const float total = __fmul_rn(ts.g, e4m3_byte_to_f32(scale_byte));
+    if (amax <= total * 0x1p20f) {  // also false for total == 0 with amax > 0
+      const bool dead = (total == 0.0f);
+      const float safe = dead ? 1.0f : total;
+      const float y = __frcp_rn(safe);
+      float q[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
+      if constexpr (kHiFirst) {
+        lo_word = f32x8_to_e2m1_word(q[0], q[1], q[2], q[3], q[4], q[5], q[6], q[7]);
+        hi_word = f32x8_to_e2m1_word(q[8], q[9], q[10], q[11], q[12], q[13], q[14], q[15]);
+      } else {
+        lo_word = f32x8_to_e2m1_word(q[1], q[0], q[3], q[2], q[5], q[4], q[7], q[6]);
+        hi_word = f32x8_to_e2m1_word(q[9], q[8], q[11], q[10], q[13], q[12], q[15], q[14]);
+      }
+      if (dead) {  // zero scale: every code is +0
+        lo_word = 0;
+        hi_word = 0;
+      }
+      return;
+    }
+  }
+  nvfp4_block<false>(v, ts.g, kHiFirst, lo_word, hi_word, scale_byte);
 }
 
 }  // namespace quant

@@ -105,6 +105,8 @@ __global__ void __launch_bounds__(kThreads)
 quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_scale, uint8_t* __restrict__ codes,
                       uint8_t* __restrict__ scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
                       int64_t num_cols, int64_t sc_pad, int hi_first) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t sc = blockIdx.y * kColsPerBlock + threadIdx.x;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + threadIdx.y;
   const int64_t n_sc = num_cols >> 4;
@@ -122,6 +124,67 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
     *reinterpret_cast<uint2*>(codes + row * (num_cols >> 1) + sc * 8) = make_uint2(lo, hi);
   }
   store_scale_quad(scales, row, sc, sc_pad >> 2, scale_byte, sc < sc_pad);
+}
+
+// Streaming variant for 16-bit inputs whose rows are whole pairs of scale blocks (32
+// elements) and need no padding of the data: a thread owns two adjacent blocks of one row
+// (two 256-bit loads, one 128-bit code store), the two lanes that share a 4-byte scale group
+// merge with one shuffle, per-thread constants (tensor scale, its reciprocal) are set up
+// once, and a block of 32 x 8 threads walks row groups with a grid stride so that every SM
+// holds the same amount of work.
+#ifndef CK_Q_MINBLOCKS
+#define CK_Q_MINBLOCKS 4
+#endif
+constexpr int kPairRows = 8;  // rows per thread block; 32 lanes x 2 blocks x 16 = 1024 columns per warp
+
+template <typename T, bool kHiFirst>
+__global__ void __launch_bounds__(32 * kPairRows, CK_Q_MINBLOCKS)
+quantize_nvfp4_pair_kernel(const T* __restrict__ x, const float* __restrict__ global_scale,
+                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int rows, int cols,
+                           int rows_pad, int sc_pad, int row_groups) {
+  pdl_launch_dependents();
+  const int pc = blockIdx.y * 32 + threadIdx.x;  // scale columns 2*pc and 2*pc + 1
+  const bool has_data = pc < (cols >> 5);
+  const bool has_scale = (threadIdx.x & 1) == 0 && 2 * pc < sc_pad;
+  pdl_wait();  // the tensor scale and x may come from the kernel before this one
+  const TensorScale ts = make_tensor_scale(__ldg(global_scale));
+  const int col_tiles = sc_pad >> 2;
+  const int code_pitch = cols >> 1;
+  // The loads of the next row group are issued before the arithmetic of the current one, so
+  // memory stays busy while the warps compute.
+  Vec256 a = {}, b = {};
+  {
+    const int row = blockIdx.x * kPairRows + threadIdx.y;
+    if (has_data && row < rows) {
+      const T* src = x + static_cast<int64_t>(row) * cols + pc * 32;
+      a = ld_global_stream_256(src);
+      b = ld_global_stream_256(src + 16);
+    }
+  }
+  for (int rg = blockIdx.x; rg < row_groups; rg += gridDim.x) {
+    const int row = rg * kPairRows + threadIdx.y;
+    const int next_row = row + gridDim.x * kPairRows;
+    Vec256 an = {}, bn = {};
+    if (has_data && next_row < rows) {
+      const T* src = x + static_cast<int64_t>(next_row) * cols + pc * 32;
+      an = ld_global_stream_256(src);
+      bn = ld_global_stream_256(src + 16);
+    }
+    uint32_t sb = 0;
+    if (has_data && row < rows) {
+      uint32_t w0, w1, w2, w3, s0, s1;
+      nvfp4_block_packed<T, kHiFirst>(a.w, ts, w0, w1, s0);
+      nvfp4_block_packed<T, kHiFirst>(b.w, ts, w2, w3, s1);
+      *reinterpret_cast<uint4*>(codes + static_cast<int64_t>(row) * code_pitch + pc * 16) = make_uint4(w0, w1, w2, w3);
+      sb = s0 | (s1 << 8);
+    }
+    const uint32_t word = sb | (__shfl_xor_sync(0xFFFFFFFFu, sb, 1) << 16);
+    if (has_scale && row < rows_pad) {
+      *reinterpret_cast<uint32_t*>(scales + swizzled_scale_offset(row, 2 * pc, col_tiles)) = word;
+    }
+    a = an;
+    b = bn;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -149,6 +212,8 @@ template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads)
 quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
                       int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols, int64_t sc_pad) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t sc = blockIdx.y * kColsPerBlock + threadIdx.x;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + threadIdx.y;
   const int64_t n_sc = num_cols >> 5;
@@ -223,9 +288,34 @@ int launch_nvfp4(const void* input, const float* gs, void* codes, void* scales, 
   uint8_t* c = static_cast<uint8_t*>(codes);
   uint8_t* s = static_cast<uint8_t*>(scales);
   const bool exact = use_exact_division();
-#define CK_LAUNCH(VEC, FAST)                                                                          \
-  quantize_nvfp4_kernel<T, VEC, FAST><<<grid, block, 0, stream>>>(                                    \
-      x, gs, c, s, orig_rows, orig_cols, num_rows, num_cols, sc_pad, hi_first)
+  if constexpr (sizeof(T) == 2) {
+    if (vec && !exact && num_cols % 32 == 0 && reinterpret_cast<uintptr_t>(codes) % 16 == 0 &&
+        num_rows < (1 << 30) && num_cols < (1 << 30)) {
+      const int rows_pad = static_cast<int>(round_up(num_rows, 128));
+      const int row_groups = rows_pad / kPairRows;
+      const int col_chunks = static_cast<int>(ceil_div(sc_pad, 64));
+      auto kernel = hi_first ? quantize_nvfp4_pair_kernel<T, true> : quantize_nvfp4_pair_kernel<T, false>;
+      // All blocks resident at once and all of the same length: the grid is the number of
+      // row groups divided into the fewest equal passes that fit the device.
+      static std::atomic<int> blocks_per_sm[2] = {{0}, {0}};
+      int per_sm = blocks_per_sm[hi_first ? 1 : 0].load(std::memory_order_relaxed);
+      if (per_sm == 0) {
+        CK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kPairRows, 0));
+        per_sm = max(per_sm, 1);
+        blocks_per_sm[hi_first ? 1 : 0].store(per_sm, std::memory_order_relaxed);
+      }
+      const int per_wave = max(1, sm_count() * per_sm / col_chunks);
+      const int waves = static_cast<int>(ceil_div(row_groups, per_wave));
+      const int grid_x = static_cast<int>(ceil_div(row_groups, waves));
+      const dim3 pgrid(static_cast<unsigned>(grid_x), static_cast<unsigned>(col_chunks)), pblock(32, kPairRows);
+      CK_CUDA(launch_pdl(kernel, pgrid, pblock, 0, stream, x, gs, c, s, static_cast<int>(num_rows),
+                         static_cast<int>(num_cols), rows_pad, static_cast<int>(sc_pad), row_groups));
+      return CK_OK;
+    }
+  }
+#define CK_LAUNCH(VEC, FAST)                                                                                  \
+  CK_CUDA(launch_pdl(quantize_nvfp4_kernel<T, VEC, FAST>, grid, block, 0, stream, x, gs, c, s, orig_rows, orig_cols, \
+                     num_rows, num_cols, sc_pad, hi_first))
   if (vec) {
     if (exact) CK_LAUNCH(true, false); else CK_LAUNCH(true, true);
   } else {
@@ -250,12 +340,12 @@ int launch_mxfp8(const void* input, void* data, void* scales, int64_t orig_rows,
   uint8_t* d = static_cast<uint8_t*>(data);
   uint8_t* s = static_cast<uint8_t*>(scales);
   if (vec) {
-    quantize_mxfp8_kernel<T, true><<<grid, block, 0, stream>>>(x, d, s, orig_rows, orig_cols, num_rows, num_cols,
-                                                               sc_pad);
+    CK_CUDA(launch_pdl(quantize_mxfp8_kernel<T, true>, grid, block, 0, stream, x, d, s, orig_rows, orig_cols, num_rows,
+                       num_cols, sc_pad));
   } else {
     CK_REQUIRE(reinterpret_cast<uintptr_t>(data) % 32 == 0, "quantize_mxfp8: output must be 32-byte aligned");
-    quantize_mxfp8_kernel<T, false><<<grid, block, 0, stream>>>(x, d, s, orig_rows, orig_cols, num_rows, num_cols,
-                                                                sc_pad);
+    CK_CUDA(launch_pdl(quantize_mxfp8_kernel<T, false>, grid, block, 0, stream, x, d, s, orig_rows, orig_cols, num_rows,
+                       num_cols, sc_pad));
   }
   CK_CUDA(cudaGetLastError());
   return CK_OK;
