@@ -55,6 +55,10 @@ _SIGNATURES = {
     "ck_nvfp4_tensor_scale_noalloc": [_P, _I, _L, _P, _P],
     "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
     "ck_debug_resident_pairs": [],
+    "ck_scaled_mm_nvfp4_allgather": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
+    "ck_scaled_mm_mxfp8_allgather": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
+    "ck_peer_barrier": [_P, _I, _I, ctypes.c_uint32, _P],
+    "ck_peer_status": [_P],
     "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],
     "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
 }
@@ -277,6 +281,76 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
                                       _stream(dev)), "scaled_mm_nvfp4")
     del bias_keep
     return out
+
+
+def _pointer_array(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def scaled_mm_nvfp4_allgather(a, b, tensor_scale_a, tensor_scale_b, block_scale_a, block_scale_b, out_ptrs, n_total: int,
+                              col_offset: int, bias=None, out_dtype: torch.dtype = torch.bfloat16, alpha=None) -> None:
+    """This rank's [M, N_local] block of a column-sharded NVFP4 GEMM, stored by the epilogue into every
+    rank's [M, n_total] buffer (``out_ptrs``: device addresses valid in this process) at ``col_offset``.
+    Launch only; the caller runs :func:`peer_barrier` behind it."""
+    lib = load_library()
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    m, ka = a.shape
+    n, kb = b.shape
+    assert ka == kb, "Matrix dimensions do not match"
+    k = 2 * ka
+    sk = roundup(k // 16, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    assert a.is_contiguous() and b.is_contiguous() and block_scale_a.is_contiguous() and block_scale_b.is_contiguous()
+    dev = a.device
+    tsa = _scalar_f32(tensor_scale_a, dev, "tensor_scale_a")
+    tsb = _scalar_f32(tensor_scale_b, dev, "tensor_scale_b")
+    alpha_t = None if alpha is None else _scalar_f32(alpha, dev, "alpha")
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    arr = _pointer_array(out_ptrs)
+    with torch.cuda.device(dev):
+        _check(lib.ck_scaled_mm_nvfp4_allgather(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa),
+                                                _ptr(tsb), _ptr(alpha_t), bias_ptr, bias_code, arr, len(out_ptrs),
+                                                DTYPE_TO_CODE[out_dtype], m, n, k, n_total, col_offset, _stream(dev)),
+               "scaled_mm_nvfp4_allgather")
+    del bias_keep
+
+
+def scaled_mm_mxfp8_allgather(a, b, block_scale_a, block_scale_b, out_ptrs, n_total: int, col_offset: int, bias=None,
+                              out_dtype: torch.dtype = torch.bfloat16) -> None:
+    """MXFP8 counterpart of :func:`scaled_mm_nvfp4_allgather`."""
+    lib = load_library()
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    m, k = a.shape
+    n, kb = b.shape
+    assert k == kb, "Matrix dimensions do not match"
+    assert a.is_contiguous() and b.is_contiguous() and block_scale_a.is_contiguous() and block_scale_b.is_contiguous()
+    dev = a.device
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    arr = _pointer_array(out_ptrs)
+    with torch.cuda.device(dev):
+        _check(lib.ck_scaled_mm_mxfp8_allgather(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), bias_ptr,
+                                                bias_code, arr, len(out_ptrs), DTYPE_TO_CODE[out_dtype], m, n, k, n_total,
+                                                col_offset, _stream(dev)), "scaled_mm_mxfp8_allgather")
+    del bias_keep
+
+
+def peer_barrier(flag_ptrs, rank: int, epoch: int, device) -> None:
+    """Launch the cross-GPU barrier kernel on the current stream of ``device`` (see ck_peer_barrier)."""
+    lib = load_library()
+    arr = _pointer_array(flag_ptrs)
+    with torch.cuda.device(device):
+        _check(lib.ck_peer_barrier(arr, rank, len(flag_ptrs), epoch & 0xFFFFFFFF, _stream(device)), "peer_barrier")
+
+
+def peer_status() -> int:
+    """Synchronise and return the barrier status word (0 = all barriers completed); clears it."""
+    lib = load_library()
+    v = ctypes.c_int(0)
+    _check(lib.ck_peer_status(ctypes.byref(v)), "peer_status")
+    return v.value
 
 
 ACTIVATIONS = {None: 0, "none": 0, "gelu_tanh": 1}

@@ -126,5 +126,81 @@ def sharded_linear_mxfp8(qx: torch.Tensor, x_block_scale: torch.Tensor, weight: 
     return gather_columns(y_local, weight.n_total, group) if gather else y_local
 
 
+class PeerOutput:
+    """Result buffers [M, N] of every rank, mapped into every process, for the GEMM whose epilogue
+    does the all-gather itself.
+
+    Allocation goes through ``torch.distributed._symmetric_memory`` (one process per GPU, NCCL
+    group): ``buffers`` result matrices used round-robin plus one array of barrier flags.  A
+    result may be read after :meth:`barrier` has run behind the GEMM on the same stream; with two
+    or more buffers a rank can still be reading result i while its peers already write result
+    i + 1.  Multicast mappings are not needed (all stores are plain peer stores).
+    """
+
+    def __init__(self, m: int, n_total: int, dtype: torch.dtype, device, group=None, buffers: int = 2):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.m, self.n_total, self.dtype, self.device = m, n_total, dtype, device
+        self.tensors, self.ptrs, self._handles = [], [], []
+        for _ in range(buffers):
+            t = symm.empty((m, n_total), dtype=dtype, device=device)
+            h = symm.rendezvous(t, self.group)
+            self.tensors.append(t)
+            self.ptrs.append([int(p) for p in h.buffer_ptrs])
+            self._handles.append(h)
+        self.flags = symm.empty((64,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        fh = symm.rendezvous(self.flags, self.group)
+        self._handles.append(fh)
+        self.flag_ptrs = [int(p) for p in fh.buffer_ptrs]
+        self.epoch = 0
+        self.turn = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # every rank's flags are zero before anyone signals
+
+    def next_buffer(self) -> tuple[torch.Tensor, list[int]]:
+        i = self.turn % len(self.tensors)
+        self.turn += 1
+        return self.tensors[i], self.ptrs[i]
+
+    def barrier(self) -> None:
+        """Launch the bounded cross-GPU barrier on the current stream."""
+        from .backends import cuda as backend
+
+        self.epoch += 1
+        backend.peer_barrier(self.flag_ptrs, self.rank, self.epoch, self.device)
+
+
+def sharded_linear_nvfp4_fused(qx: torch.Tensor, x_scale: torch.Tensor, x_block_scale: torch.Tensor,
+                               weight: ShardedQuantizedWeight, peers: PeerOutput,
+                               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """y[M, N] = linear(x, W), W column-sharded, with the all-gather done by the GEMM epilogue: every
+    output tile is stored straight into all ranks' result buffers over NVLink while the tensor cores
+    work on the next tile, followed by one cross-GPU barrier.  Returns this rank's full [M, N] result
+    (a view of one of ``peers``' buffers, valid in stream order)."""
+    from .backends import cuda as backend
+
+    out, ptrs = peers.next_buffer()
+    backend.scaled_mm_nvfp4_allgather(qx, weight.qdata, x_scale, weight.tensor_scale, x_block_scale, weight.block_scale,
+                                      ptrs, weight.n_total, weight.start, bias=weight.bias, out_dtype=out_dtype)
+    peers.barrier()
+    return out
+
+
+def sharded_linear_mxfp8_fused(qx: torch.Tensor, x_block_scale: torch.Tensor, weight: ShardedQuantizedWeight,
+                               peers: PeerOutput, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """MXFP8 counterpart of :func:`sharded_linear_nvfp4_fused`."""
+    from .backends import cuda as backend
+
+    out, ptrs = peers.next_buffer()
+    backend.scaled_mm_mxfp8_allgather(qx, weight.qdata, x_block_scale, weight.block_scale, ptrs, weight.n_total,
+                                      weight.start, bias=weight.bias, out_dtype=out_dtype)
+    peers.barrier()
+    return out
+
+
 def padded_scale_rows(n: int) -> int:
     return roundup(n, SHARD_GRANULE)

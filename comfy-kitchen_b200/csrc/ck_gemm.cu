@@ -120,6 +120,7 @@ struct GemmParams {
   int n_row_blocks_b;      // ceil(N / 128)
   int tiles_m, tiles_n;
   int out_tma;             // the output qualifies for TMA stores (16-byte aligned base and pitch)
+  int n_out;               // destinations of every output tile (1, or one per GPU of an all-gather)
   int* status;             // device status word: set non-zero when a wait gave up
   // fused epilogue (FUSED kernels only)
   int activation;          // CK_ACT_*
@@ -129,6 +130,14 @@ struct GemmParams {
 };
 
 __device__ int g_gemm_status = 0;
+
+// Destinations of the output tile: one tensor map for a plain GEMM; for the column-sharded
+// GEMM with a fused all-gather, one per GPU - each a window [M, N_local] at this rank's column
+// offset inside that GPU's full [M, N_total] result (peer memory mapped into this process).
+constexpr int kMaxOutputs = 8;
+struct OutputMaps {
+  CUtensorMap m[kMaxOutputs];
+};
 
 // Optional per-tile timeline (SM cycle counter) for tuning; compiled in with -DCK_GEMM_TRACE only.
 #ifdef CK_GEMM_TRACE
@@ -257,7 +266,7 @@ template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename Out
 __global__ void __launch_bounds__(num_threads(FUSED, TILE_N, CTAS), 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                         const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+                         const __grid_constant__ OutputMaps maps_out, const GemmParams p) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OUT_STAGE>;
   static_assert(!(FUSED && OUT_STAGE != 0), "the fused epilogue stores from registers");
   constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N, CTAS);
@@ -298,7 +307,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
-    if constexpr (OUT_STAGE != 0) prefetch_tensormap(&map_out);
+    if constexpr (OUT_STAGE != 0) {
+      for (int d = 0; d < p.n_out; ++d) prefetch_tensormap(&maps_out.m[d]);
+    }
   }
   if (warp == 1) tmem_alloc<CTAS>(tmem_base_slot, kTmemCols);
   tc_fence_before_sync();
@@ -613,7 +624,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #else
                 if (lane == 0 && row0 < p.M && col < p.N) {
 #endif
-                  tma_store_2d_addr(&map_out, stage_box, col, row0);
+                  // the same staged box goes to every destination (peer stores cross NVLink)
+                  for (int d = 0; d < p.n_out; ++d) tma_store_2d_addr(&maps_out.m[d], stage_box, col, row0);
                 }
                 // (an empty group when nothing was stored keeps the ring's group count in step)
                 if (lane == 0) bulk_commit_group();
@@ -684,7 +696,15 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (warp == 2) CK_TRACE(9);
     }
     if constexpr (OUT_STAGE != 0) {
-      if (lane == 0) bulk_wait_group_read0();  // shared memory stays valid until the last store has read it
+      // shared memory stays valid until the last store has read it; stores to other GPUs are
+      // waited for to the end, so that they precede whatever follows this kernel on the stream
+      if (lane == 0) {
+        if (p.n_out > 1) {
+          bulk_wait_group0();
+        } else {
+          bulk_wait_group_read0();
+        }
+      }
     }
   }
 
@@ -758,12 +778,12 @@ int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64
 
 // Row-major [rows, cols] output of `elem_bytes`-wide elements: boxes of 32 rows x 128 bytes,
 // 128-byte swizzle (the layout the epilogue stages its rows in).
-int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes) {
+int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes, int64_t pitch_elems) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const CUtensorMapDataType type = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * elem_bytes};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * elem_bytes};
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), 32};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult r = fn(map, type, 2, base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -772,8 +792,19 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, in
   return CK_OK;
 }
 
+// Where the output goes (host side): `n` buffers (1 = plain GEMM), each holding this GEMM's
+// [M, N] block at column `col_offset` of a row-major matrix with `pitch` columns.
+struct OutputSpec {
+  void* const* ptrs = nullptr;
+  int n = 1;
+  int64_t pitch = 0;
+  int64_t col_offset = 0;
+  bool plain(int64_t N) const { return n == 1 && pitch == N && col_offset == 0; }
+};
+
 template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED, int OUT_STAGE = 0>
-int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, cudaStream_t stream) {
+int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, const OutputSpec& os,
+                  cudaStream_t stream) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OUT_STAGE>;
   auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT, FUSED, OUT_STAGE>;
   // the dynamic shared-memory opt-in is per device: do it once for each device that launches
@@ -823,17 +854,27 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
     if (int rc = make_scale_map(&map_sfa, p.sfa, p.n_row_blocks_a, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
     if (int rc = make_scale_map(&map_sfb, p.sfb, p.n_row_blocks_b, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
   }
-  CUtensorMap map_out = {};
+  OutputMaps maps_out = {};
   p.out_tma = 0;
+  p.n_out = 1;
   if constexpr (OUT_STAGE != 0) {
-    // TMA stores need a 16-byte aligned base and row pitch; other outputs take the register path
-    if (p.out != nullptr && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 &&
-        (static_cast<int64_t>(p.N) * sizeof(OutT)) % 16 == 0) {
-      if (int rc = make_output_map(&map_out, p.out, p.M, p.N, sizeof(OutT))) return rc;
+    // TMA stores need 16-byte aligned bases and row pitch; other outputs take the register path
+    bool ok = p.out != nullptr && (os.pitch * static_cast<int64_t>(sizeof(OutT))) % 16 == 0 &&
+              (os.col_offset * static_cast<int64_t>(sizeof(OutT))) % 16 == 0;
+    for (int d = 0; ok && d < os.n; ++d) ok = os.ptrs[d] != nullptr && reinterpret_cast<uintptr_t>(os.ptrs[d]) % 16 == 0;
+    if (ok) {
+      for (int d = 0; d < os.n; ++d) {
+        void* base = static_cast<uint8_t*>(os.ptrs[d]) + os.col_offset * static_cast<int64_t>(sizeof(OutT));
+        if (int rc = make_output_map(&maps_out.m[d], base, p.M, p.N, sizeof(OutT), os.pitch)) return rc;
+      }
       p.out_tma = 1;
+      p.n_out = os.n;
     }
   }
-  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, map_out, p));
+  if (p.out_tma == 0 && !os.plain(p.N)) {
+    return fail(CK_ERR_INVALID_ARGUMENT, "strided or multiple outputs need 16-byte aligned buffers, pitch and column offset");
+  }
+  CK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, maps_out, p));
   return CK_OK;
 }
 
@@ -848,7 +889,7 @@ int forced_config() {
 
 template <Kind KIND, typename OutT, bool FUSED>
 int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[4], const GemmParams& p,
-                     cudaStream_t stream) {
+                     const OutputSpec& os, cudaStream_t stream) {
   // map_b[0|1|2|3] have boxes of 128 | 192 | 256 | 96 rows.
   int config = forced_config();
   if (config == 0) {
@@ -862,23 +903,25 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[4], co
       config = 1;
     }
   }
+  // strided / multiple destinations exist only in the configurations with a staged epilogue
+  if (!os.plain(p.N) && config != 4 && config != 6) config = 1;
   switch (config) {
     case 6:
-      if constexpr (!FUSED) return launch_config<KIND, 256, 1, 4, 2, OutT, false, 2>(map_a, map_b[0], p, stream);
+      if constexpr (!FUSED) return launch_config<KIND, 256, 1, 4, 2, OutT, false, 2>(map_a, map_b[0], p, os, stream);
       [[fallthrough]];
     case 5:
-      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 5, 2, OutT, false, 1>(map_a, map_b[3], p, stream);
+      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 5, 2, OutT, false, 1>(map_a, map_b[3], p, os, stream);
       [[fallthrough]];
     case 4:
-      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED, FUSED ? 0 : 1>(map_a, map_b[0], p, stream);
+      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED, FUSED ? 0 : 1>(map_a, map_b[0], p, os, stream);
     case 3:
-      return launch_config<KIND, 256, 1, 4, 1, OutT, FUSED>(map_a, map_b[2], p, stream);
+      return launch_config<KIND, 256, 1, 4, 1, OutT, FUSED>(map_a, map_b[2], p, os, stream);
     case 2:
-      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 4, 1, OutT, false>(map_a, map_b[1], p, stream);
+      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 4, 1, OutT, false>(map_a, map_b[1], p, os, stream);
       [[fallthrough]];  // the fused epilogue needs 64-column warp shares: no 192-wide variant
     default:
-      if constexpr (!FUSED) return launch_config<KIND, 128, 2, 5, 1, OutT, false, 1>(map_a, map_b[0], p, stream);
-      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, stream);
+      if constexpr (!FUSED) return launch_config<KIND, 128, 2, 5, 1, OutT, false, 1>(map_a, map_b[0], p, os, stream);
+      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, os, stream);
   }
 }
 
@@ -893,7 +936,8 @@ struct FusedArgs {
 template <Kind KIND>
 int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, const void* sfb, const float* tsa,
               const float* tsb, const float* alpha, const void* bias, int bias_dtype, void* out, int out_dtype,
-              int64_t M, int64_t N, int64_t K, void* stream, const FusedArgs& fused = FusedArgs()) {
+              int64_t M, int64_t N, int64_t K, void* stream, const FusedArgs& fused = FusedArgs(),
+              const OutputSpec* out_spec = nullptr) {
   CK_REQUIRE(a && b && sfa && sfb, "%s: null pointer", op);
   CK_REQUIRE(out != nullptr || (fused.enabled && fused.rq_codes != nullptr), "%s: no output requested", op);
   if (fused.enabled) {
@@ -952,25 +996,39 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   if (int rc = make_operand_map(&map_b[2], b, N, p.k_bytes, 256)) return rc;
   if (int rc = make_operand_map(&map_b[3], b, N, p.k_bytes, 96)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  OutputSpec os;
+  void* const single[1] = {out};
+  if (out_spec != nullptr) {
+    os = *out_spec;
+    CK_REQUIRE(!fused.enabled, "%s: the fused epilogue has one plain output", op);
+    CK_REQUIRE(os.n >= 1 && os.n <= kMaxOutputs && os.ptrs != nullptr, "%s: 1..%d output buffers", op, kMaxOutputs);
+    CK_REQUIRE(os.col_offset >= 0 && os.col_offset + N <= os.pitch, "%s: columns [%lld, %lld) outside a pitch of %lld", op,
+               (long long)os.col_offset, (long long)(os.col_offset + N), (long long)os.pitch);
+  } else {
+    os.ptrs = single;
+    os.n = 1;
+    os.pitch = N;
+    os.col_offset = 0;
+  }
   if constexpr (KIND == Kind::kNvfp4) {
     if (fused.enabled) {
       switch (out_dtype) {
         case CK_DTYPE_BF16:
-          return launch_for_shape<KIND, __nv_bfloat16, true>(map_a, map_b, p, s);
+          return launch_for_shape<KIND, __nv_bfloat16, true>(map_a, map_b, p, os, s);
         case CK_DTYPE_F16:
-          return launch_for_shape<KIND, __half, true>(map_a, map_b, p, s);
+          return launch_for_shape<KIND, __half, true>(map_a, map_b, p, os, s);
         default:
-          return launch_for_shape<KIND, float, true>(map_a, map_b, p, s);
+          return launch_for_shape<KIND, float, true>(map_a, map_b, p, os, s);
       }
     }
   }
   switch (out_dtype) {
     case CK_DTYPE_BF16:
-      return launch_for_shape<KIND, __nv_bfloat16, false>(map_a, map_b, p, s);
+      return launch_for_shape<KIND, __nv_bfloat16, false>(map_a, map_b, p, os, s);
     case CK_DTYPE_F16:
-      return launch_for_shape<KIND, __half, false>(map_a, map_b, p, s);
+      return launch_for_shape<KIND, __half, false>(map_a, map_b, p, os, s);
     default:
-      return launch_for_shape<KIND, float, false>(map_a, map_b, p, s);
+      return launch_for_shape<KIND, float, false>(map_a, map_b, p, os, s);
   }
 }
 
@@ -1005,6 +1063,37 @@ extern "C" int ck_linear_nvfp4_fused(const void* a, const void* b, const void* s
   f.rq_scale = requant_scale;
   return ck::scaled_mm<ck::Kind::kNvfp4>("linear_nvfp4_fused", a, b, sfa, sfb, tensor_scale_a, tensor_scale_b, alpha, bias,
                                          bias_dtype, out, out_dtype, M, N, K, stream, f);
+}
+
+extern "C" int ck_scaled_mm_nvfp4_allgather(const void* a, const void* b, const void* sfa, const void* sfb,
+                                            const float* tensor_scale_a, const float* tensor_scale_b, const float* alpha,
+                                            const void* bias, int bias_dtype, void* const* out_ptrs, int world,
+                                            int out_dtype, int64_t M, int64_t N_local, int64_t K, int64_t n_total,
+                                            int64_t col_offset, void* stream) {
+  ck::OutputSpec os;
+  os.ptrs = out_ptrs;
+  os.n = world;
+  os.pitch = n_total;
+  os.col_offset = col_offset;
+  CK_REQUIRE(out_ptrs != nullptr && world >= 1 && world <= ck::kMaxOutputs, "scaled_mm_nvfp4_allgather: 1..%d destinations",
+             ck::kMaxOutputs);
+  return ck::scaled_mm<ck::Kind::kNvfp4>("scaled_mm_nvfp4_allgather", a, b, sfa, sfb, tensor_scale_a, tensor_scale_b, alpha,
+                                         bias, bias_dtype, out_ptrs[0], out_dtype, M, N_local, K, stream, ck::FusedArgs(), &os);
+}
+
+extern "C" int ck_scaled_mm_mxfp8_allgather(const void* a, const void* b, const void* sfa, const void* sfb,
+                                            const void* bias, int bias_dtype, void* const* out_ptrs, int world,
+                                            int out_dtype, int64_t M, int64_t N_local, int64_t K, int64_t n_total,
+                                            int64_t col_offset, void* stream) {
+  ck::OutputSpec os;
+  os.ptrs = out_ptrs;
+  os.n = world;
+  os.pitch = n_total;
+  os.col_offset = col_offset;
+  CK_REQUIRE(out_ptrs != nullptr && world >= 1 && world <= ck::kMaxOutputs, "scaled_mm_mxfp8_allgather: 1..%d destinations",
+             ck::kMaxOutputs);
+  return ck::scaled_mm<ck::Kind::kMxfp8>("scaled_mm_mxfp8_allgather", a, b, sfa, sfb, nullptr, nullptr, nullptr, bias,
+                                         bias_dtype, out_ptrs[0], out_dtype, M, N_local, K, stream, ck::FusedArgs(), &os);
 }
 
 // Number of CTA pairs the 256x256 configuration runs concurrently on the current device

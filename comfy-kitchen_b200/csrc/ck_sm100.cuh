@@ -173,6 +173,8 @@ __device__ __forceinline__ void tma_store_2d_addr(const CUtensorMap* map, uint32
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once the bulk stores committed by this thread have finished READING shared memory.
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Returns once they have completed entirely (writes performed).
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // ... until at most kPending of them are still reading.
 template <int kPending>
 __device__ __forceinline__ void bulk_wait_group_read() {

@@ -210,6 +210,50 @@ CK_API int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa, con
                        void* out, int out_dtype,
                        int64_t M, int64_t N, int64_t K, void* stream);
 
+/* ------------------------------------------------------------------ multi-GPU (one node) */
+/*
+ * Column-sharded GEMM with the all-gather of the output fused into the epilogue.  No
+ * counterpart in the reference, which has no multi-device code; the operand arguments are
+ * those of ck_scaled_mm_nvfp4 / ck_scaled_mm_mxfp8 for this rank's shard of the weight
+ * (b: [N_local, K], its own tiled scales, its slice of the bias).
+ *
+ * Every output tile is written to `world` destinations: out_ptrs[d] (HOST array of device
+ * pointers) is the full row-major [M, n_total] result buffer of rank d, mapped into this
+ * process (peer memory); the tile lands at columns [col_offset, col_offset + N_local).  The
+ * stores are plain (non-multicast) bulk tensor stores, so the transfer over NVLink overlaps
+ * the tensor-core work tile by tile.  Buffers, n_total and col_offset must keep 16-byte
+ * alignment (col_offset and n_total multiples of 8 for 16-bit outputs).
+ *
+ * The call only launches.  The results are complete on every rank once each rank has run
+ * ck_peer_barrier behind its GEMM on the same stream.
+ */
+CK_API int ck_scaled_mm_nvfp4_allgather(const void* a, const void* b, const void* block_scale_a,
+                                 const void* block_scale_b, const float* tensor_scale_a,
+                                 const float* tensor_scale_b, const float* alpha, const void* bias,
+                                 int bias_dtype, void* const* out_ptrs, int world, int out_dtype,
+                                 int64_t M, int64_t N_local, int64_t K, int64_t n_total,
+                                 int64_t col_offset, void* stream);
+CK_API int ck_scaled_mm_mxfp8_allgather(const void* a, const void* b, const void* block_scale_a,
+                                 const void* block_scale_b, const void* bias, int bias_dtype,
+                                 void* const* out_ptrs, int world, int out_dtype, int64_t M,
+                                 int64_t N_local, int64_t K, int64_t n_total, int64_t col_offset,
+                                 void* stream);
+
+/*
+ * Barrier between the GPUs of one node over peer-mapped flags.  flag_ptrs[r] (HOST array of
+ * device pointers) is rank r's array of `world` 32-bit flags, zero before the first use and
+ * mapped into every process.  `epoch` must grow by one per barrier (all ranks pass the same
+ * value).  The kernel orders this rank's earlier stores on the stream (peer stores included)
+ * before its signal, and returns when every rank has signalled this epoch - or after about a
+ * second, in which case it records the missing rank (ck_peer_status) instead of hanging.
+ * Each rank launches it on its own GPU.  No counterpart in the reference.
+ */
+CK_API int ck_peer_barrier(void* const* flag_ptrs, int rank, int world, uint32_t epoch, void* stream);
+
+/* Synchronises the current device and reports (then clears) the barrier status word:
+ * 0 = every barrier completed, 1 + r = rank r did not arrive in time.  Host pointer. */
+CK_API int ck_peer_status(int* status_out);
+
 /* Diagnostic with no counterpart in the reference: how many 2-CTA clusters of the
  * 256x256 GEMM configuration can be resident at once on the current device
  * (negative on error). */
