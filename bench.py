@@ -371,12 +371,32 @@ def run_sharded_gemm(args, torch, ck, dist, device, rank, world, clocks_cls, loc
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # The fused path (epilogue stores into every rank's peer-mapped result + one barrier kernel)
+    # needs torch's symmetric memory; when that is unavailable only the NCCL path is timed.
+    peers, fused_error = None, None
+    if dist is not None and world > 1:
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            peers = sharded.PeerOutput(m, n, torch.bfloat16, device, buffers=2)
+        except Exception as e:  # noqa: BLE001 - reported in the JSON line
+            fused_error = f"{type(e).__name__}: {e}"[:200]
     with clocks_cls(local_rank) as clocks:
         ms_gemm = timed(lambda: sharded.sharded_linear_nvfp4(qx, sx, bsx, shard, gather=False), args.steps, args.warmup)
-        ms_full = timed(lambda: sharded.sharded_linear_nvfp4(qx, sx, bsx, shard), args.steps, args.warmup)
+        ms_nccl = timed(lambda: sharded.sharded_linear_nvfp4(qx, sx, bsx, shard), args.steps, args.warmup)
+        ms_fused = None
+        if peers is not None:
+            ms_fused = timed(lambda: sharded.sharded_linear_nvfp4_fused(qx, sx, bsx, shard, peers), args.steps, args.warmup)
     y = sharded.sharded_linear_nvfp4(qx, sx, bsx, shard)
     y_local = sharded.sharded_linear_nvfp4(qx, sx, bsx, shard, gather=False)
     ok = bool(torch.equal(y[:, shard.start:shard.end], y_local)) and tuple(y.shape) == (m, n)
+    fused_ok, barrier_status = None, None
+    if peers is not None:
+        from comfy_kitchen.backends import cuda as backend
+
+        yf = sharded.sharded_linear_nvfp4_fused(qx, sx, bsx, shard, peers)
+        fused_ok = bool(torch.equal(yf, y))
+        barrier_status = backend.peer_status()
+    ms_full = ms_fused if ms_fused is not None else ms_nccl
     if rank != 0:
         return None
     flops = 2.0 * m * n * k
@@ -385,13 +405,22 @@ def run_sharded_gemm(args, torch, ck, dist, device, rank, world, clocks_cls, loc
         "metric": "sharded_nvfp4_gemm_tflops", "value": flops / (ms_full * 1e-3) / 1e12, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"NVFP4 GEMM M={m} N={n} K={k}, N column-sharded over {world} GPUs + NCCL all-gather of bf16 output",
+        "config": {"workload": f"NVFP4 GEMM M={m} N={n} K={k}, N column-sharded over {world} GPUs, all-gather of the bf16 "
+                               + ("output fused into the GEMM epilogue (peer stores over NVLink + barrier kernel)"
+                                  if ms_fused is not None else "output by NCCL"),
                    "M": m, "N": n, "K": k},
         "gemm_only": {"ms": ms_gemm, "aggregate_tflops": flops / (ms_gemm * 1e-3) / 1e12},
-        "all_gather": {"bytes_received_per_gpu": recv, "ms": max(ms_full - ms_gemm, 0.0),
-                       "gbs_per_gpu": (recv / ((ms_full - ms_gemm) * 1e-3) / 1e9) if ms_full > ms_gemm else None,
-                       "nvlink_peak_gbs": 770.0},
-        "gathered_equals_local": ok, "clocks": clocks.summary(), "gpu_launches": args.steps,
+        "nccl_all_gather": {"ms_gemm_plus_gather": ms_nccl, "tflops": flops / (ms_nccl * 1e-3) / 1e12,
+                            "bytes_received_per_gpu": recv,
+                            "gbs_per_gpu": (recv / ((ms_nccl - ms_gemm) * 1e-3) / 1e9) if ms_nccl > ms_gemm else None},
+        "fused_all_gather": None if ms_fused is None else {
+            "ms": ms_fused, "tflops": flops / (ms_fused * 1e-3) / 1e12, "equals_nccl_result": fused_ok,
+            "barrier_status": barrier_status,
+            # roofline of the fused kernel: the slower of tensor time and the bytes this GPU must push
+            "nvlink_floor_ms": recv / 770.0e9 * 1e3, "nvlink_peak_gbs": 770.0,
+            "frac_of_floor": max(recv / 770.0e9 * 1e3, ms_gemm) / ms_fused},
+        "fused_unavailable": fused_error,
+        "gathered_equals_local": ok, "clocks": clocks.summary(), "gpu_launches": args.steps * (2 if ms_fused is not None else 1),
     }
 
 
