@@ -45,9 +45,10 @@ constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
 // Epilogue warps per CTA: two per 32-lane quarter of tensor memory for the plain epilogue,
 // four for the fused one (its activation + quantization arithmetic is ~30 instructions per
 // element and must keep up with the tensor pipe).
-// A CTA pair with 192-wide tiles uses three (64 columns each, whole 128-byte store boxes).
+// A CTA pair with 192-wide tiles uses three (64 columns each, whole 128-byte store boxes), a
+// 64-wide tile one.
 constexpr int epilogue_warps(bool fused, int tile_n, int ctas) {
-  return (fused && tile_n >= 256) ? 16 : (ctas == 2 && tile_n == 192) ? 12 : 8;
+  return (fused && tile_n >= 256) ? 16 : (ctas == 2 && tile_n == 192) ? 12 : (tile_n <= 64) ? 4 : 8;
 }
 constexpr int num_threads(bool fused, int tile_n, int ctas) {
   return 64 + 32 * epilogue_warps(fused, tile_n, ctas);  // + TMA, MMA warps
@@ -882,15 +883,16 @@ int forced_config() {
   // CK_GEMM_CONFIG pins the kernel configuration (tuning aid); unset = choose by shape.
   //   1 = one CTA, 128 x 128 tiles      2 = one CTA, 128 x 192 tiles (two accumulators)
   //   3 = one CTA, 128 x 256 tiles      4 = CTA pair, 256 x 256 tiles
-  //   5 = CTA pair, 256 x 192 tiles (two accumulators)
+  //   5 = CTA pair, 256 x 192 tiles (two accumulators)   6 = as 4 with 4 stages and two store boxes
+  //   7 = one CTA, 128 x 64 tiles (small problems: twice the CTAs of 1)
   const char* e = getenv("CK_GEMM_CONFIG");
   return e ? atoi(e) : 0;
 }
 
 template <Kind KIND, typename OutT, bool FUSED>
-int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[4], const GemmParams& p,
+int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[5], const GemmParams& p,
                      const OutputSpec& os, cudaStream_t stream) {
-  // map_b[0|1|2|3] have boxes of 128 | 192 | 256 | 96 rows.
+  // map_b[0|1|2|3|4] have boxes of 128 | 192 | 256 | 96 | 64 rows.
   int config = forced_config();
   if (config == 0) {
     const int64_t pair_tiles = ceil_div(p.M, 256) * ceil_div(p.N, 256);
@@ -899,13 +901,18 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[4], co
       config = 4;
     } else if (tiles256 >= sm_count()) {
       config = 3;
+    } else if (ceil_div(p.M, kTileM) * ceil_div(p.N, 128) * 4 <= sm_count()) {
+      config = 7;  // so few 128 x 128 tiles that halving them still leaves SMs idle: more, smaller CTAs
     } else {
       config = 1;
     }
   }
   // strided / multiple destinations exist only in the configurations with a staged epilogue
-  if (!os.plain(p.N) && config != 4 && config != 6) config = 1;
+  if (!os.plain(p.N) && config != 4 && config != 6 && config != 7) config = 1;
   switch (config) {
+    case 7:
+      if constexpr (!FUSED) return launch_config<KIND, 64, 2, 6, 1, OutT, false, 1>(map_a, map_b[4], p, os, stream);
+      [[fallthrough]];
     case 6:
       if constexpr (!FUSED) return launch_config<KIND, 256, 1, 4, 2, OutT, false, 2>(map_a, map_b[0], p, os, stream);
       [[fallthrough]];
@@ -989,12 +996,13 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
 
-  CUtensorMap map_a, map_b[4];
+  CUtensorMap map_a, map_b[5];
   if (int rc = make_operand_map(&map_a, a, M, p.k_bytes, kTileM)) return rc;
   if (int rc = make_operand_map(&map_b[0], b, N, p.k_bytes, 128)) return rc;
   if (int rc = make_operand_map(&map_b[1], b, N, p.k_bytes, 192)) return rc;
   if (int rc = make_operand_map(&map_b[2], b, N, p.k_bytes, 256)) return rc;
   if (int rc = make_operand_map(&map_b[3], b, N, p.k_bytes, 96)) return rc;
+  if (int rc = make_operand_map(&map_b[4], b, N, p.k_bytes, 64)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   OutputSpec os;
   void* const single[1] = {out};
