@@ -912,7 +912,7 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[5], co
   switch (config) {
     case 7:
       if constexpr (!FUSED) return launch_config<KIND, 64, 2, 6, 1, OutT, false, 1>(map_a, map_b[4], p, os, stream);
-      [[fallthrough]];
+      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, os, stream);
     case 6:
       if constexpr (!FUSED) return launch_config<KIND, 256, 1, 4, 2, OutT, false, 2>(map_a, map_b[0], p, os, stream);
       [[fallthrough]];
