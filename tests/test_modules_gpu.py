@@ -1,0 +1,163 @@
+"""Quantized nn.Linear replacements, model patcher and offline weight quantizer
+(reference behaviour: samples/nvfp4_linear.py, samples/mxfp8_model_patcher.py)."""
+import pytest
+import torch
+import torch.nn as nn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ck(cuda_device):
+    import comfy_kitchen
+
+    info = comfy_kitchen.list_backends()["cuda"]
+    assert info["available"], f"cuda backend not loaded: {info['unavailable_reason']}"
+    return comfy_kitchen
+
+
+def _dense(cuda_device, i=256, o=384, bias=True, seed=0):
+    torch.manual_seed(seed)
+    lin = nn.Linear(i, o, bias=bias, device=cuda_device, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.mul_(0.5)
+    return lin
+
+
+def test_nvfp4_linear_equals_the_operator_sequence(ck, cuda_device):
+    from comfy_kitchen.modules import NVFP4Linear
+
+    lin = _dense(cuda_device)
+    q = NVFP4Linear.from_linear(lin)
+    x = torch.randn(96, 256, device=cuda_device, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        y = q(x)
+    sx = (x.abs().amax() / 2688).float()
+    sw = (lin.weight.detach().abs().amax() / 2688).float()
+    qx, bsx = ck.quantize_nvfp4(x, sx)
+    qw, bsw = ck.quantize_nvfp4(lin.weight.detach(), sw)
+    ref = ck.scaled_mm_nvfp4(qx, qw, sx, sw, bsx, bsw, bias=lin.bias.detach(), out_dtype=torch.bfloat16)
+    assert torch.equal(y, ref)
+    dense = lin(x)
+    rel = ((y.float() - dense.float()).norm() / dense.float().norm()).item()
+    assert rel < 0.2  # FP4 quantization error of both operands, not a kernel tolerance
+
+
+def test_nvfp4_linear_state_dict_round_trip_and_keys(ck, cuda_device):
+    from comfy_kitchen.modules import NVFP4Linear
+
+    lin = _dense(cuda_device)
+    q = NVFP4Linear.from_linear(lin, input_scale=0.004)
+    sd = q.state_dict()
+    assert set(sd) == {"weight", "weight_scale", "weight_scale_2", "bias", "input_scale"}
+    assert sd["weight"].dtype == torch.uint8 and tuple(sd["weight"].shape) == (384, 128)
+    # block scales may be stored as raw bytes (float8 support in checkpoint formats is spotty)
+    sd["weight_scale"] = sd["weight_scale"].view(torch.uint8).reshape(-1).cpu()
+    fresh = NVFP4Linear(256, 384, device=cuda_device, dtype=torch.bfloat16)
+    result = fresh.load_state_dict({k: v.clone() for k, v in sd.items()})
+    assert not result.missing_keys and not result.unexpected_keys
+    x = torch.randn(4, 40, 256, device=cuda_device, dtype=torch.bfloat16)  # 3-D input
+    with torch.inference_mode():
+        a, b = q(x), fresh(x)
+    assert a.shape == (4, 40, 384)
+    assert torch.equal(a, b)
+
+
+def test_nvfp4_linear_without_input_scale_is_dynamic(ck, cuda_device):
+    from comfy_kitchen.modules import NVFP4Linear
+
+    q = NVFP4Linear.from_linear(_dense(cuda_device, bias=False))
+    sd = q.state_dict()
+    assert "input_scale" not in sd and "bias" not in sd
+    fresh = NVFP4Linear(256, 384, bias=False, device=cuda_device, dtype=torch.bfloat16)
+    fresh.load_state_dict(sd)
+    assert fresh.input_scale is None
+    x = torch.randn(32, 256, device=cuda_device, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        assert torch.equal(q(x), fresh(x))
+
+
+def test_load_reports_missing_and_malformed_entries(ck, cuda_device):
+    from comfy_kitchen.modules import NVFP4Linear
+
+    fresh = NVFP4Linear(256, 384, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="weight_scale_2"):
+        fresh.load_state_dict({"weight": torch.zeros(384, 128, dtype=torch.uint8),
+                               "weight_scale": torch.zeros(384 * 16, dtype=torch.uint8),
+                               "bias": torch.zeros(384, dtype=torch.bfloat16)})
+    with pytest.raises(RuntimeError, match="tiled layout"):
+        fresh.load_state_dict({"weight": torch.zeros(384, 128, dtype=torch.uint8),
+                               "weight_scale": torch.zeros(7, dtype=torch.uint8),
+                               "weight_scale_2": torch.ones(1), "bias": torch.zeros(384, dtype=torch.bfloat16)})
+
+
+def test_mxfp8_linear_round_trip(ck, cuda_device):
+    from comfy_kitchen.modules import MXFP8Linear
+
+    lin = _dense(cuda_device)
+    q = MXFP8Linear.from_linear(lin)
+    sd = q.state_dict()
+    assert set(sd) == {"weight", "weight_scale", "bias"}
+    fresh = MXFP8Linear(256, 384, device=cuda_device, dtype=torch.bfloat16)
+    fresh.load_state_dict({k: (v.view(torch.uint8) if k != "bias" else v) for k, v in sd.items()})
+    x = torch.randn(2, 33, 256, device=cuda_device, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        a, b = q(x), fresh(x)
+    assert torch.equal(a, b) and a.shape == (2, 33, 384)
+    qx, bsx = ck.quantize_mxfp8(x.reshape(-1, 256), pad_32x=True)
+    qw, bsw = ck.quantize_mxfp8(lin.weight.detach())
+    ref = ck.scaled_mm_mxfp8(qx, qw, bsx, bsw, bias=lin.bias.detach(), out_dtype=torch.bfloat16)[:66]
+    assert torch.equal(a.reshape(-1, 384), ref)
+
+
+class _Tiny(nn.Module):
+    def __init__(self, dev):
+        super().__init__()
+        kw = dict(device=dev, dtype=torch.bfloat16)
+        self.inp = nn.Linear(128, 256, **kw)
+        self.blocks = nn.ModuleList([nn.Sequential(nn.Linear(256, 512, **kw), nn.GELU(approximate="tanh"),
+                                                   nn.Linear(512, 256, **kw)) for _ in range(2)])
+        self.head = nn.Linear(256, 24, **kw)   # too small
+        self.odd = nn.Linear(200, 256, **kw)   # in_features % 32 != 0 (but % 16 != 0 too: 200 % 16 = 8)
+
+    def forward(self, x):
+        x = self.inp(x)
+        for b in self.blocks:
+            x = x + b(x)
+        return self.head(x)
+
+
+@pytest.mark.parametrize("layout", ["nvfp4", "mxfp8"])
+def test_patch_model(ck, cuda_device, layout):
+    from comfy_kitchen.modules import MXFP8Linear, NVFP4Linear, patch_model
+
+    torch.manual_seed(1)
+    model = _Tiny(cuda_device)
+    x = torch.randn(3, 50, 128, device=cuda_device, dtype=torch.bfloat16)
+    dense = model(x)
+    model, report = patch_model(model, layout=layout, skip_names=["blocks.1.2"])
+    cls = NVFP4Linear if layout == "nvfp4" else MXFP8Linear
+    assert isinstance(model.inp, cls) and isinstance(model.blocks[0][0], cls) and isinstance(model.blocks[1][0], cls)
+    assert isinstance(model.blocks[1][2], nn.Linear) and isinstance(model.head, nn.Linear) and isinstance(model.odd, nn.Linear)
+    assert sorted(report["patched"]) == ["blocks.0.0", "blocks.0.2", "blocks.1.0", "inp"]
+    assert set(report["skipped"]) == {"blocks.1.2", "head", "odd"}
+    with torch.inference_mode():
+        y = model(x)
+    assert y.shape == dense.shape
+    rel = ((y.float() - dense.float()).norm() / dense.float().norm()).item()
+    assert rel < (0.35 if layout == "nvfp4" else 0.1)
+
+
+def test_quantize_state_dict_feeds_the_layer(ck, cuda_device):
+    from comfy_kitchen.modules import NVFP4Linear, quantize_state_dict
+
+    lin = _dense(cuda_device)
+    sd = quantize_state_dict({"fc.weight": lin.weight.detach().cpu(), "fc.bias": lin.bias.detach().cpu(),
+                              "norm.weight": torch.ones(256)}, layout="nvfp4", device=cuda_device)
+    assert set(sd) == {"fc.weight", "fc.weight_scale", "fc.weight_scale_2", "fc.bias", "norm.weight"}
+    assert sd["fc.weight_scale"].dtype == torch.uint8 and not sd["fc.weight"].is_cuda
+    holder = nn.ModuleDict({"fc": NVFP4Linear(256, 384, device=cuda_device, dtype=torch.bfloat16)})
+    holder.load_state_dict({k: v for k, v in sd.items() if k.startswith("fc.")})
+    x = torch.randn(64, 256, device=cuda_device, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        assert torch.equal(holder["fc"](x), NVFP4Linear.from_linear(lin)(x))
