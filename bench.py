@@ -499,6 +499,62 @@ def run_mlp_pair(args, torch, ck, backend, device, clocks_cls, local_rank) -> di
     }
 
 
+def run_mmdit(args, torch, dist, device, rank, world, clocks_cls, local_rank) -> dict | None:
+    """Random-init MMDiT-shaped stack, every block linear through NVFP4 QuantizedTensors, batch 8 split
+    data-parallel over the ranks (strong scaling, no collective inside the forward)."""
+    import bench_mmdit as mm
+    from comfy_kitchen.modules import NVFP4Linear
+
+    cfg = mm.MMDiTConfig()
+    if args.mmdit_blocks:
+        d, s_ = (int(v) for v in args.mmdit_blocks.split(","))
+        cfg.double_blocks, cfg.single_blocks = d, s_
+    total_batch = 8
+    if total_batch % world != 0:
+        raise SystemExit("--case mmdit splits a batch of 8: use 1, 2, 4 or 8 GPUs")
+    batch = total_batch // world
+    with torch.inference_mode():
+        model = mm.MMDiTStack(cfg, device, NVFP4Linear.from_linear, seed=0)
+        img, txt, vec = mm.make_inputs(cfg, batch, device, seed=rank)
+        steps, warmup = min(args.steps, 8), min(max(args.warmup, 1), 3)
+        for _ in range(warmup):
+            out = model(img, txt, vec)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with clocks_cls(local_rank) as clocks:
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                out = model(img, txt, vec)
+            e1.record()
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+        finite = bool(torch.isfinite(out.float()).all().item())
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank != 0:
+        return None
+    tokens = total_batch * (cfg.img_tokens + cfg.txt_tokens)
+    n_linear = cfg.double_blocks * 10 + cfg.single_blocks * 3
+    return {
+        "metric": "mmdit_forward_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 linears (e2m1 x ue4m3, fp32 accumulate), bf16 attention", "data": "synthetic",
+        "config": {"workload": f"random-init MMDiT-shaped stack: hidden {cfg.hidden}, {cfg.heads} heads, {cfg.double_blocks} double + "
+                               f"{cfg.single_blocks} single blocks, {cfg.img_tokens}+{cfg.txt_tokens} tokens, batch {total_batch} "
+                               f"split over {world} GPU(s); dynamic activation scales",
+                   "linear_params": cfg.linear_params, "batch_per_gpu": batch},
+        "linear_tflops": cfg.linear_flops(total_batch) / (ms * 1e-3) / 1e12,
+        "attention_tflops_in_step": cfg.attention_flops(total_batch) / (ms * 1e-3) / 1e12,
+        "output_finite": finite, "clocks": clocks.summary(), "gpu_launches": steps * n_linear * 3,
+    }
+
+
 def run_gpu_arm(args) -> dict | None:
     import torch
 
@@ -529,6 +585,11 @@ def run_gpu_arm(args) -> dict | None:
         return run_mlp_pair(args, torch, ck, backend, device, ClockSampler, local_rank) if rank == 0 else None
     if args.case == "sharded_gemm":
         line = run_sharded_gemm(args, torch, ck, dist, device, rank, world, ClockSampler, local_rank)
+        if dist is not None:
+            dist.destroy_process_group()
+        return line
+    if args.case == "mmdit":
+        line = run_mmdit(args, torch, dist, device, rank, world, ClockSampler, local_rank)
         if dist is not None:
             dist.destroy_process_group()
         return line
@@ -675,7 +736,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="linear",
                     choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
-                             "sharded_gemm", "mlp_pair"])
+                             "sharded_gemm", "mlp_pair", "mmdit"])
+    ap.add_argument("--mmdit-blocks", default="", help="double,single block counts of --case mmdit (default 19,38)")
     ap.add_argument("--shape", default="16384,15360,3072", help="M,N,K of --case sharded_gemm")
     ap.add_argument("--rows", type=int, default=0, help="override M (profiling of one kernel on a different size)")
     ap.add_argument("--ring", type=int, default=8, help="independent buffer sets cycled through (L2 defeat)")

@@ -24,9 +24,9 @@ from typing import Iterable
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from .tensor import QuantizedTensor, TensorCoreMXFP8Layout, TensorCoreNVFP4Layout
+from .tensor.blockwise import quantized_linear
 
 NVFP4 = "TensorCoreNVFP4Layout"
 MXFP8 = "TensorCoreMXFP8Layout"
@@ -65,13 +65,13 @@ class _QuantizedLinearBase(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if isinstance(x, QuantizedTensor):
-            return F.linear(x, self.weight, self.bias)
+            return quantized_linear(x, self.weight, self.bias)
         shape = x.shape
         if x.dim() != 2:
             x = x.reshape(-1, shape[-1])
         if not x.is_contiguous():
             x = x.contiguous()
-        y = F.linear(self._quantize_input(x), self.weight, self.bias)
+        y = quantized_linear(self._quantize_input(x), self.weight, self.bias)
         if len(shape) != 2:
             y = y.reshape(*shape[:-1], self.out_features)
         return y

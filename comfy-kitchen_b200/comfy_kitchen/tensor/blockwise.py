@@ -39,6 +39,27 @@ def _both_quantized_2d(a, b) -> bool:
     return isinstance(a, QuantizedTensor) and isinstance(b, QuantizedTensor) and a._qdata.dim() == 2
 
 
+def quantized_linear(x: QuantizedTensor, w: QuantizedTensor, bias: torch.Tensor | None = None,
+                     out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``linear(x, w, bias)`` on two quantized 2-D tensors of the same block-scaled layout, straight
+    through the layout's kernel - the body of the ``aten.linear`` handler without the dispatcher, for
+    callers (module ``forward``) that must reach the fast path in every grad mode: outside
+    ``torch.inference_mode()`` ``F.linear`` is decomposed into ``t`` + ``addmm`` before the tensor
+    subclass sees it."""
+    layout = x.layout_cls
+    if w.layout_cls is not layout or not _both_quantized_2d(x, w) or _is_transposed(x) or _is_transposed(w):
+        return torch.nn.functional.linear(*dequantize_args((x, w, bias)))
+    out_dtype = out_dtype or x._params.orig_dtype
+    try:
+        y = layout.scaled_mm(x, w, bias, out_dtype)
+    except (RuntimeError, TypeError) as e:
+        if strict_mode():
+            raise
+        logger.warning(f"{layout.__name__} linear failed: {e}, falling back to dequantization")
+        return torch.nn.functional.linear(*dequantize_args((x, w, bias)))
+    return crop(y, x._params.orig_shape[0], w._params.orig_shape[0])
+
+
 def install_handlers(layout, *, name: str, with_addmm: bool) -> None:
     """Register the aten.t / mm / linear (/ addmm) handlers of a block-scaled layout.
 

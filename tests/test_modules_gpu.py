@@ -161,3 +161,26 @@ def test_quantize_state_dict_feeds_the_layer(ck, cuda_device):
     x = torch.randn(64, 256, device=cuda_device, dtype=torch.bfloat16)
     with torch.inference_mode():
         assert torch.equal(holder["fc"](x), NVFP4Linear.from_linear(lin)(x))
+
+
+def test_mmdit_shaped_stack_runs_quantized(ck, cuda_device):
+    """The full-model harness of the benchmark at toy size: every block linear through NVFP4, output
+    finite and close to the same stack with dense linears."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench_mmdit as mm
+    from comfy_kitchen.modules import NVFP4Linear
+
+    cfg = mm.MMDiTConfig(hidden=256, heads=2, double_blocks=1, single_blocks=2, mlp_ratio=4, img_tokens=96, txt_tokens=32)
+    assert cfg.linear_params == (1 * 36 + 2 * 15) * 256 * 256
+    with torch.inference_mode():
+        dense = mm.MMDiTStack(cfg, cuda_device, lambda lin: lin, seed=3)
+        quant = mm.MMDiTStack(cfg, cuda_device, NVFP4Linear.from_linear, seed=3)
+        img, txt, vec = mm.make_inputs(cfg, 2, cuda_device)
+        a, b = dense(img, txt, vec), quant(img, txt, vec)
+    assert b.shape == (2, 96, 256) and torch.isfinite(b.float()).all()
+    assert all(isinstance(m, NVFP4Linear) for m in quant.modules() if hasattr(m, "in_features"))
+    rel = ((a.float() - b.float()).norm() / a.float().norm()).item()
+    assert rel < 0.3
