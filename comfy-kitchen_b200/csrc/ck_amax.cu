@@ -17,7 +17,7 @@ namespace ck {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kElemsPerThread = 32;
+constexpr int kElemsPerThread = 64;
 constexpr int kChunk = kThreads * kElemsPerThread;  // elements per block
 constexpr int kPartialOffset = 64;                  // words
 
@@ -60,22 +60,35 @@ __global__ void __launch_bounds__(kThreads)
 nvfp4_tensor_scale_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ scale_out,
                           unsigned int* __restrict__ scratch) {
   constexpr int kPerVec = 32 / sizeof(T);  // elements per 256-bit load
+  constexpr int kVecs = kElemsPerThread / kPerVec;
+  pdl_launch_dependents();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kChunk;
   float m = 0.0f;
   const bool aligned = (reinterpret_cast<uintptr_t>(x) & 31u) == 0;
+  pdl_wait();  // x may be the output of the kernel before this one
+  if (aligned && base + kChunk <= n) {
+    // whole chunk in range: all loads are issued before the first one is consumed
+    Vec256 raw[kVecs];
 #pragma unroll
-  for (int v = 0; v < kElemsPerThread / kPerVec; ++v) {
-    const int64_t i = base + (static_cast<int64_t>(v) * kThreads + threadIdx.x) * kPerVec;
-    if (aligned && i + kPerVec <= n) {
-      m = fmaxf(m, abs_max_of_vec<T>(ld_global_stream_256(x + i)));
-    } else {
-      for (int j = 0; j < kPerVec; ++j) {
-        if (i + j < n) {
-          float f;
-          if constexpr (std::is_same<T, __nv_bfloat16>::value) f = __bfloat162float(x[i + j]);
-          else if constexpr (std::is_same<T, __half>::value) f = __half2float(x[i + j]);
-          else f = x[i + j];
-          m = fmaxf(m, fabsf(f));
+    for (int v = 0; v < kVecs; ++v) {
+      raw[v] = ld_global_stream_256(x + base + (static_cast<int64_t>(v) * kThreads + threadIdx.x) * kPerVec);
+    }
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) m = fmaxf(m, abs_max_of_vec<T>(raw[v]));
+  } else {
+    for (int v = 0; v < kVecs; ++v) {
+      const int64_t i = base + (static_cast<int64_t>(v) * kThreads + threadIdx.x) * kPerVec;
+      if (aligned && i + kPerVec <= n) {
+        m = fmaxf(m, abs_max_of_vec<T>(ld_global_stream_256(x + i)));
+      } else {
+        for (int j = 0; j < kPerVec; ++j) {
+          if (i + j < n) {
+            float f;
+            if constexpr (std::is_same<T, __nv_bfloat16>::value) f = __bfloat162float(x[i + j]);
+            else if constexpr (std::is_same<T, __half>::value) f = __half2float(x[i + j]);
+            else f = x[i + j];
+            m = fmaxf(m, fabsf(f));
+          }
         }
       }
     }
@@ -121,8 +134,8 @@ int64_t blocks_for(int64_t n) { return ceil_div(n, kChunk); }
 
 template <typename T>
 void launch(const void* x, int64_t n, float* scale_out, unsigned int* scratch, cudaStream_t s) {
-  nvfp4_tensor_scale_kernel<T><<<static_cast<unsigned>(blocks_for(n)), kThreads, 0, s>>>(static_cast<const T*>(x), n,
-                                                                                       scale_out, scratch);
+  launch_pdl(nvfp4_tensor_scale_kernel<T>, dim3(static_cast<unsigned>(blocks_for(n))), dim3(kThreads), 0, s,
+             static_cast<const T*>(x), n, scale_out, scratch);
 }
 
 int run(const char* op, const void* x, int dtype, int64_t n, float* scale_out, unsigned int* scratch,
@@ -151,7 +164,7 @@ int run(const char* op, const void* x, int dtype, int64_t n, float* scale_out, u
 // caller-supplied buffer.  It exists once per GPU that loads the library and stays
 // resident until the process exits.  In host code the name below is only a handle, not a
 // device address; the address is looked up once per device (static_scratch_for_device).
-constexpr int64_t kStaticMaxBlocks = 16384;                          // 64 KiB of partials
+constexpr int64_t kStaticMaxBlocks = 8192;                           // 32 KiB of partials
 constexpr int64_t kStaticMaxElements = kStaticMaxBlocks * kChunk;    // 134 217 728 elements
 static __device__ __align__(256) unsigned int g_static_scratch[kPartialOffset + kStaticMaxBlocks];
 

@@ -120,9 +120,9 @@ CK_API int ck_nvfp4_tensor_scale(const void* input, int input_dtype, int64_t num
  * because they must not allocate device memory at that point: plugins that live inside a
  * host application with a fixed memory budget, or serving loops where a cudaMalloc would
  * stall every stream of the device.  This entry point has no counterpart in the reference.  It allocates
- * nothing: its scratch is a fixed array inside the library (about 64 KiB per GPU, resident
+ * nothing: its scratch is a fixed array inside the library (about 32 KiB per GPU, resident
  * from the moment the library is loaded on that GPU until the process exits).
- *   - Limit: num_elements <= 134 217 728 (16384 blocks of 8192 elements); larger inputs
+ *   - Limit: num_elements <= 134 217 728 (8192 blocks of 16384 elements); larger inputs
  *     are refused with CK_ERR_INVALID_ARGUMENT - use ck_nvfp4_tensor_scale instead.
  *   - The first call on each device looks up the array's device address (one-off set-up
  *     that may make the CUDA runtime load the library's kernels); make that first call
