@@ -110,13 +110,17 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference's eager path, timed on the host
 # --------------------------------------------------------------------------------------------
-def cpu_linear_once(rows: int, seed: int = 0) -> tuple[float, int]:
-    """One NVFP4 linear on `rows` rows of the workload through the numpy oracle. Returns (seconds, rows)."""
+def cpu_linear_once(rows: int, seed: int = 0) -> tuple[float, int, str]:
+    """One NVFP4 linear on `rows` rows of the workload through the CPU oracle: the C restatement
+    (OpenMP row loops) when it could be built, else the numpy one; the float32 matmul of the GEMM
+    contract is BLAS either way.  Returns (seconds, rows, which)."""
     import numpy as np
     import torch
 
     from oracle import ck_oracle as oc
+    from oracle import ck_oracle_c as occ
 
+    impl, which = (occ, "C/OpenMP oracle") if occ.available() else (oc, "numpy oracle")
     g = torch.Generator(device="cpu").manual_seed(seed)
     x = torch.randn(rows, K, generator=g)
     x = torch.where(torch.rand(rows, K, generator=g) < 0.001, x * 20, x).bfloat16()
@@ -125,12 +129,12 @@ def cpu_linear_once(rows: int, seed: int = 0) -> tuple[float, int]:
     sx = np.float32((x.abs().amax() / 2688.0).float().item())
     sw = np.float32((w.abs().amax() / 2688.0).float().item())
     xf, wf = x.float().numpy(), w.float().numpy()
-    qw, bsw = oc.quantize_nvfp4(wf, sw)  # weights are pre-quantized: not timed
+    qw, bsw = impl.quantize_nvfp4(wf, sw)  # weights are pre-quantized: not timed
     t0 = time.perf_counter()
-    qx, bsx = oc.quantize_nvfp4(xf, sx)
-    out = oc.scaled_mm_nvfp4(qx, qw, sx, sw, bsx, bsw, bias=bias)
-    oc.f32_to_bf16_bits(out)
-    return time.perf_counter() - t0, rows
+    qx, bsx = impl.quantize_nvfp4(xf, sx)
+    out = impl.scaled_mm_nvfp4(qx, qw, sx, sw, bsx, bsw, bias=bias)
+    impl.f32_to_bf16_bits(out)
+    return time.perf_counter() - t0, rows, which
 
 
 def cpu_threads() -> int:
@@ -149,12 +153,13 @@ def run_reference_arm(args) -> dict:
     for _ in range(max(1, min(args.warmup, 1))):
         cpu_linear_once(rows)
     times = []
+    which = ""
     for _ in range(args.steps):
-        dt, _ = cpu_linear_once(rows)
+        dt, _, which = cpu_linear_once(rows)
         times.append(dt)
     per_step = sum(times) / len(times)
     tflops = 2.0 * rows * N * K / per_step / 1e12
-    sample = f"{rows} of {M} rows per step (quantize_nvfp4(x) + dequantize->fp32 matmul + bias -> bf16), numpy oracle, BLAS matmul"
+    sample = f"{rows} of {M} rows per step (quantize_nvfp4(x) + dequantize->fp32 matmul + bias -> bf16), {which}, BLAS matmul"
     return {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
@@ -718,10 +723,10 @@ def run_gpu_arm(args) -> dict | None:
         _t.set_num_threads(cpu_threads())
         sample_rows = 1024
         cpu_linear_once(256)
-        dt, _ = cpu_linear_once(sample_rows)
+        dt, _, which = cpu_linear_once(sample_rows)
         line["cpu_baseline"] = {
             "value": 2.0 * sample_rows * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
-            "sample": f"{sample_rows} of {M} rows, one step: numpy oracle quantize_nvfp4(x) + dequantize->fp32 BLAS matmul + bias",
+            "sample": f"{sample_rows} of {M} rows, one step: {which} quantize_nvfp4(x) + dequantize->fp32 BLAS matmul + bias",
             "seconds": dt}
     if dist is not None:
         dist.destroy_process_group()
