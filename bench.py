@@ -514,29 +514,47 @@ def run_mmdit(args, torch, dist, device, rank, world, clocks_cls, local_rank) ->
     if args.mmdit_blocks:
         d, s_ = (int(v) for v in args.mmdit_blocks.split(","))
         cfg.double_blocks, cfg.single_blocks = d, s_
-    total_batch = 8
+    total_batch = args.mmdit_batch
     if total_batch % world != 0:
-        raise SystemExit("--case mmdit splits a batch of 8: use 1, 2, 4 or 8 GPUs")
+        raise SystemExit(f"--case mmdit splits a batch of {total_batch}: the GPU count must divide it")
     batch = total_batch // world
+    use_graph = not args.no_graph
     with torch.inference_mode():
         model = mm.MMDiTStack(cfg, device, NVFP4Linear.from_linear, seed=0)
         img, txt, vec = mm.make_inputs(cfg, batch, device, seed=rank)
         steps, warmup = min(args.steps, 8), min(max(args.warmup, 1), 3)
-        for _ in range(warmup):
-            out = model(img, txt, vec)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with clocks_cls(local_rank) as clocks:
-            if dist is not None:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(steps):
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
                 out = model(img, txt, vec)
-            e1.record()
-            torch.cuda.synchronize()
-            if dist is not None:
-                dist.barrier()
+            stream.synchronize()
+            graph = None
+            if use_graph:
+                # static shapes: the whole forward (every kernel of the library is launch-only) is
+                # captured once and replayed, which takes the per-layer host work off the step
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        out = model(img, txt, vec)
+                    graph.replay()
+                    stream.synchronize()
+                except Exception as e:  # noqa: BLE001 - reported in the JSON line
+                    graph, use_graph = None, f"capture failed: {type(e).__name__}: {e}"[:160]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with clocks_cls(local_rank) as clocks:
+                if dist is not None:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                e0.record(stream)
+                for _ in range(steps):
+                    if graph is not None:
+                        graph.replay()
+                    else:
+                        out = model(img, txt, vec)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                if dist is not None:
+                    dist.barrier()
         finite = bool(torch.isfinite(out.float()).all().item())
     t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
     if dist is not None:
@@ -553,7 +571,7 @@ def run_mmdit(args, torch, dist, device, rank, world, clocks_cls, local_rank) ->
         "config": {"workload": f"random-init MMDiT-shaped stack: hidden {cfg.hidden}, {cfg.heads} heads, {cfg.double_blocks} double + "
                                f"{cfg.single_blocks} single blocks, {cfg.img_tokens}+{cfg.txt_tokens} tokens, batch {total_batch} "
                                f"split over {world} GPU(s); dynamic activation scales",
-                   "linear_params": cfg.linear_params, "batch_per_gpu": batch},
+                   "linear_params": cfg.linear_params, "batch_per_gpu": batch, "cuda_graph": use_graph},
         "linear_tflops": cfg.linear_flops(total_batch) / (ms * 1e-3) / 1e12,
         "attention_tflops_in_step": cfg.attention_flops(total_batch) / (ms * 1e-3) / 1e12,
         "output_finite": finite, "clocks": clocks.summary(), "gpu_launches": steps * n_linear * 3,
@@ -743,6 +761,7 @@ def main():
                     choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
                              "sharded_gemm", "mlp_pair", "mmdit"])
     ap.add_argument("--mmdit-blocks", default="", help="double,single block counts of --case mmdit (default 19,38)")
+    ap.add_argument("--mmdit-batch", type=int, default=8, help="total batch of --case mmdit, split over the GPUs")
     ap.add_argument("--shape", default="16384,15360,3072", help="M,N,K of --case sharded_gemm")
     ap.add_argument("--rows", type=int, default=0, help="override M (profiling of one kernel on a different size)")
     ap.add_argument("--ring", type=int, default=8, help="independent buffer sets cycled through (L2 defeat)")

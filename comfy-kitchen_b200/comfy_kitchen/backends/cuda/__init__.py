@@ -95,6 +95,11 @@ def load_library():
     return lib
 
 
+def is_loaded() -> bool:
+    """True once the C-ABI library has been loaded in this process (never tries to load it)."""
+    return _lib is not None
+
+
 def _check(rc: int, what: str):
     if rc != 0:
         msg = _lib.ck_last_error()

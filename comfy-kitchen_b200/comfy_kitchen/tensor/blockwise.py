@@ -24,6 +24,18 @@ def strict_mode() -> bool:
     return os.environ.get("CK_STRICT", "0") == "1"
 
 
+def direct_backend(*tensors):
+    """The CUDA backend module when the kernels can be called without the operator dispatcher: all
+    tensors on a CUDA device and nothing is being traced.  ``ck.<op>`` goes through a custom op and
+    the backend registry (what ``torch.compile`` needs, and what CPU tensors need to raise the
+    documented error); eager CUDA calls from the layouts skip those ~50 us of host work per call."""
+    if torch.compiler.is_compiling() or not all(t.is_cuda for t in tensors if isinstance(t, torch.Tensor)):
+        return None
+    from comfy_kitchen.backends import cuda as backend
+
+    return backend if backend.is_loaded() else None
+
+
 def crop(result: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
     """Cut a padded matmul result back to the logical output shape."""
     if result.shape[0] != rows or result.shape[1] != cols:

@@ -10,7 +10,7 @@ import comfy_kitchen as ck
 from comfy_kitchen.float_utils import roundup
 
 from .base import BaseLayoutParams, QuantizedLayout
-from .blockwise import install_handlers
+from .blockwise import direct_backend, install_handlers
 
 
 class TensorCoreMXFP8Layout(QuantizedLayout):
@@ -37,7 +37,11 @@ class TensorCoreMXFP8Layout(QuantizedLayout):
             raise ValueError(f"MXFP8 requires 2D tensor, got {tensor.dim()}D")
         orig_shape = tuple(tensor.shape)
         pad = cls.get_padded_shape(orig_shape) != orig_shape
-        qdata, block_scale = ck.quantize_mxfp8(tensor, pad_32x=pad)
+        backend = direct_backend(tensor) if tensor.is_contiguous() else None
+        if backend is not None:
+            qdata, block_scale = backend.quantize_mxfp8(tensor, pad_32x=pad)
+        else:
+            qdata, block_scale = ck.quantize_mxfp8(tensor, pad_32x=pad)
         return qdata, cls.Params(scale=block_scale, orig_dtype=tensor.dtype, orig_shape=orig_shape)
 
     @classmethod
@@ -70,6 +74,9 @@ class TensorCoreMXFP8Layout(QuantizedLayout):
     def scaled_mm(cls, a, b, bias, out_dtype):
         qa, sa = cls.get_plain_tensors(a)
         qb, sb = cls.get_plain_tensors(b)
+        backend = direct_backend(qa, qb, bias)
+        if backend is not None:
+            return backend.scaled_mm_mxfp8(qa, qb, sa, sb, bias=bias, out_dtype=out_dtype)
         return ck.scaled_mm_mxfp8(qa, qb, block_scale_a=sa, block_scale_b=sb, bias=bias, out_dtype=out_dtype)
 
 

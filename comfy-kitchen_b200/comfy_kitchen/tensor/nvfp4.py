@@ -10,7 +10,7 @@ import comfy_kitchen as ck
 from comfy_kitchen.float_utils import F4_E2M1_MAX, F8_E4M3_MAX, roundup
 
 from .base import BaseLayoutParams, QuantizedLayout
-from .blockwise import install_handlers
+from .blockwise import direct_backend, install_handlers
 
 
 class TensorCoreNVFP4Layout(QuantizedLayout):
@@ -57,7 +57,11 @@ class TensorCoreNVFP4Layout(QuantizedLayout):
             scale = torch.tensor(scale)
         scale = scale.to(device=tensor.device, dtype=torch.float32)
         pad = cls.get_padded_shape(orig_shape) != orig_shape
-        qdata, block_scale = ck.quantize_nvfp4(tensor, scale, pad_16x=pad)
+        backend = direct_backend(tensor) if tensor.is_contiguous() else None
+        if backend is not None:
+            qdata, block_scale = backend.quantize_nvfp4(tensor, scale, pad_16x=pad)
+        else:
+            qdata, block_scale = ck.quantize_nvfp4(tensor, scale, pad_16x=pad)
         return qdata, cls.Params(scale=scale, orig_dtype=tensor.dtype, orig_shape=orig_shape, block_scale=block_scale)
 
     @classmethod
@@ -91,6 +95,9 @@ class TensorCoreNVFP4Layout(QuantizedLayout):
     def scaled_mm(cls, a, b, bias, out_dtype):
         qa, sa, bsa = cls.get_plain_tensors(a)
         qb, sb, bsb = cls.get_plain_tensors(b)
+        backend = direct_backend(qa, qb, bias)
+        if backend is not None:
+            return backend.scaled_mm_nvfp4(qa, qb, sa, sb, bsa, bsb, bias=bias, out_dtype=out_dtype)
         return ck.scaled_mm_nvfp4(qa, qb, tensor_scale_a=sa, tensor_scale_b=sb, block_scale_a=bsa, block_scale_b=bsb,
                                   bias=bias, out_dtype=out_dtype)
 
