@@ -47,8 +47,11 @@ constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
 // element and must keep up with the tensor pipe).
 // A CTA pair with 192-wide tiles uses three (64 columns each, whole 128-byte store boxes), a
 // 64-wide tile one.
+#ifndef CK_FUSED_WARPS
+#define CK_FUSED_WARPS 16
+#endif
 constexpr int epilogue_warps(bool fused, int tile_n, int ctas) {
-  return (fused && tile_n >= 256) ? 16 : (ctas == 2 && tile_n == 192) ? 12 : (tile_n <= 64) ? 4 : 8;
+  return (fused && tile_n >= 256) ? CK_FUSED_WARPS : (ctas == 2 && tile_n == 192) ? 12 : (tile_n <= 64) ? 4 : 8;
 }
 constexpr int num_threads(bool fused, int tile_n, int ctas) {
   return 64 + 32 * epilogue_warps(fused, tile_n, ctas);  // + TMA, MMA warps
@@ -232,6 +235,29 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[32],
   }
 }
 
+// Two floats rounded to a 16-bit OutT and packed (first value in the low half), and back.
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+    __nv_bfloat162 q = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&q);
+  } else {
+    __half2 q = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&q);
+  }
+}
+template <typename OutT>
+__device__ __forceinline__ void unpack_pair(uint32_t w, float& lo, float& hi) {
+  if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xFFFF0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+}
+
 template <typename OutT>
 __device__ __forceinline__ float round_to_out(float x) {
   if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
@@ -331,7 +357,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   // asynchronous instructions themselves are issued by one elected lane.
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    uint32_t it = 0;
+    [[maybe_unused]] uint32_t it = 0;
+    int ring_s = 0;
+    uint32_t ring_ph = 0;
     [[maybe_unused]] uint32_t tile_it = 0;
     for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
       // consecutive workers take tiles that share the B columns (tile_m fastest)
@@ -348,8 +376,13 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(m0 / kTileM) * p.sf_col_tiles * 512;
       const uint8_t* sfb_src = p.sfb + static_cast<int64_t>(rb_b0) * p.sf_col_tiles * 512;
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+        // ring position and phase as running counters (STAGES is not a power of two)
+        const int s = ring_s;
+        const uint32_t ph = ring_ph;
+        if (++ring_s == STAGES) {
+          ring_s = 0;
+          ring_ph ^= 1u;
+        }
         if constexpr (CTAS == 2) {
           mbar_wait_cluster(&empty_bar[s], ph ^ 1, abort_flag);  // signalled from the leader CTA
         } else {
@@ -417,7 +450,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t acc_full_addr = smem_u32(acc_full_bar);
     const uint32_t empty_addr_peer = (CTAS == 2) ? map_to_cta(empty_addr, 1) : 0u;
     const uint32_t acc_full_addr_peer = (CTAS == 2) ? map_to_cta(acc_full_addr, 1) : 0u;
-    uint32_t it = 0;
+    [[maybe_unused]] uint32_t it = 0;
+    int ring_s = 0;
+    uint32_t ring_ph = 0;
+    uint32_t sf_ring = 0;
     uint32_t tile_it = 0;
     for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
       const int n0 = (tile / p.tiles_m) * TILE_N;
@@ -427,8 +463,14 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
       const uint32_t sfb_shift = (n0 % 128) / 32;
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+        const int s = ring_s;
+        const uint32_t ph = ring_ph;
+        if (++ring_s == STAGES) {
+          ring_s = 0;
+          ring_ph ^= 1u;
+        }
+        const uint32_t sf_buf = sf_ring * Cfg::kSfColsPerBuf;
+        if (++sf_ring == Cfg::kSfBufs) sf_ring = 0;
         CK_TRACE2(1, it);
         if constexpr (CTAS == 2) {
           mbar_wait_cluster(&full_bar[s], ph, abort_flag);
@@ -449,7 +491,6 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
           const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
           const int n_mma = min(kMmaPerStage, total_mma - ks * kMmaPerStage);
-          const uint32_t sf_buf = (it % Cfg::kSfBufs) * Cfg::kSfColsPerBuf;
           const uint32_t t_sfa = t_sfa0 + sf_buf;
           const uint32_t t_sfb = t_sfb0 + sf_buf;
           const uint32_t t_sfb_tile = t_sfb + sfb_shift;
@@ -653,43 +694,118 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int rq_col_tiles = (p.N / 16 + 3) / 4;
         const int rows_pad = (p.M + 127) / 128 * 128;
         uint32_t scale_word = 0;
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const int col = n0 + c0 + c * 32;
-          const int valid = min(32, p.N - col);
-          if (valid <= 0) continue;
-          float v[32];
-          if (row < p.M) {
-            scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float y = round_to_out<OutT>(v[i]);
-              if (p.activation == CK_ACT_GELU_TANH) y = round_to_out<OutT>(gelu_tanh(y));
-              v[i] = y;
-            }
-            if (p.out != nullptr) store_row_chunk<OutT>(out_row + c * 32, v, valid, vec_ok);
-          }
-          if (p.rq_codes != nullptr) {
+        bool packed_path = false;
+        if constexpr (sizeof(OutT) == 2) packed_path = (n0 + c0 + kColsPerWarp <= p.N);
+        if (packed_path) {
+          if constexpr (sizeof(OutT) == 2) {
+            // 16-bit outputs, whole chunks: the values an unfused caller would see are the
+            // accumulators rounded to OutT, so they are kept as packed pairs from here on (half
+            // the registers), the activation works pair by pair, and the re-quantization runs on
+            // the packed words exactly as the stand-alone quantizer does.
+            const quant::TensorScale rq_ts = quant::make_tensor_scale(rq_g);
+            uint32_t pk[kChunks][16];
             if (row < p.M) {
-              float lo16[16], hi16[16];
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                lo16[i] = v[i];
-                hi16[i] = v[16 + i];
+              for (int c = 0; c < kChunks; ++c) {
+                const float2* b2 = reinterpret_cast<const float2*>(bias_s + c0 + c * 32);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const float2 b = b2[i];
+                  pk[c][i] = pack_pair<OutT>(fmaf(__uint_as_float(buf[c][2 * i]), alpha, b.x),
+                                             fmaf(__uint_as_float(buf[c][2 * i + 1]), alpha, b.y));
+                }
               }
-              uint32_t w0, w1, w2, w3, s0, s1;
-              quant::nvfp4_block<true>(lo16, rq_g, true, w0, w1, s0);
-              quant::nvfp4_block<true>(hi16, rq_g, true, w2, w3, s1);
-              *reinterpret_cast<uint4*>(p.rq_codes + static_cast<int64_t>(row) * (p.N >> 1) + (col >> 1)) =
-                  make_uint4(w0, w1, w2, w3);
-              scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
             }
-            if ((c & 1) && row < rows_pad) {
-              // rows between M and the next multiple of 128 are padding of the scale tensor: zero
-              // this chunk and the previous one cover scale columns (col/16 - 2) .. (col/16 + 1)
-              const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
-              *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
-              scale_word = 0;
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+              const int col = n0 + c0 + c * 32;
+              if (row < p.M) {
+                if (p.activation == CK_ACT_GELU_TANH) {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) {
+                    float a, b;
+                    unpack_pair<OutT>(pk[c][i], a, b);
+                    pk[c][i] = pack_pair<OutT>(gelu_tanh(a), gelu_tanh(b));
+                  }
+                }
+                if (p.out != nullptr) {
+                  if (vec_ok) {
+                    Vec256 o0, o1;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                      o0.w[i] = pk[c][i];
+                      o1.w[i] = pk[c][8 + i];
+                    }
+                    st_global_256(out_row + c * 32, o0);
+                    st_global_256(out_row + c * 32 + 16, o1);
+                  } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t*>(out_row + c * 32 + 2 * i) = pk[c][i];
+                  }
+                }
+              }
+              if (p.rq_codes != nullptr) {
+                if (row < p.M) {
+                  uint32_t lo[8], hi[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    lo[i] = pk[c][i];
+                    hi[i] = pk[c][8 + i];
+                  }
+                  uint32_t w0, w1, w2, w3, s0, s1;
+                  quant::nvfp4_block_packed<OutT, true>(lo, rq_ts, w0, w1, s0);
+                  quant::nvfp4_block_packed<OutT, true>(hi, rq_ts, w2, w3, s1);
+                  *reinterpret_cast<uint4*>(p.rq_codes + static_cast<int64_t>(row) * (p.N >> 1) + (col >> 1)) =
+                      make_uint4(w0, w1, w2, w3);
+                  scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
+                }
+                if ((c & 1) && row < rows_pad) {
+                  const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
+                  *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
+                  scale_word = 0;
+                }
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            const int col = n0 + c0 + c * 32;
+            const int valid = min(32, p.N - col);
+            if (valid <= 0) continue;
+            float v[32];
+            if (row < p.M) {
+              scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float y = round_to_out<OutT>(v[i]);
+                if (p.activation == CK_ACT_GELU_TANH) y = round_to_out<OutT>(gelu_tanh(y));
+                v[i] = y;
+              }
+              if (p.out != nullptr) store_row_chunk<OutT>(out_row + c * 32, v, valid, vec_ok);
+            }
+            if (p.rq_codes != nullptr) {
+              if (row < p.M) {
+                float lo16[16], hi16[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  lo16[i] = v[i];
+                  hi16[i] = v[16 + i];
+                }
+                uint32_t w0, w1, w2, w3, s0, s1;
+                quant::nvfp4_block<true>(lo16, rq_g, true, w0, w1, s0);
+                quant::nvfp4_block<true>(hi16, rq_g, true, w2, w3, s1);
+                *reinterpret_cast<uint4*>(p.rq_codes + static_cast<int64_t>(row) * (p.N >> 1) + (col >> 1)) =
+                    make_uint4(w0, w1, w2, w3);
+                scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
+              }
+              if ((c & 1) && row < rows_pad) {
+                // rows between M and the next multiple of 128 are padding of the scale tensor: zero
+                // this chunk and the previous one cover scale columns (col/16 - 2) .. (col/16 + 1)
+                const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
+                *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
+                scale_word = 0;
+              }
             }
           }
         }

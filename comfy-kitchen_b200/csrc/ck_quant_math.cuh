@@ -179,11 +179,8 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float g) {
   return t;
 }
 
-template <typename T, bool kHiFirst>
-__device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const TensorScale& ts, uint32_t& lo_word,
-                                                   uint32_t& hi_word, uint32_t& scale_byte) {
-  static_assert(sizeof(T) == 2, "packed 16-bit inputs");
-  float v[16];
+template <typename T>
+__device__ __forceinline__ void widen16(const uint32_t (&w)[8], float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
@@ -195,6 +192,30 @@ __device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const
       v[2 * i + 1] = f.y;
     }
   }
+}
+
+// The IEEE-division path of a packed block, out of line: it is taken only outside the
+// exactness window (tiny or huge scales), and keeping it out of the caller's body keeps the
+// caller's register allocation that of the common path.  Arguments and result travel in
+// registers (words by value, a small struct back).
+struct BlockCodes {
+  uint32_t lo, hi, scale_byte;
+};
+template <typename T, bool kHiFirst>
+__device__ __noinline__ BlockCodes nvfp4_block_packed_ieee(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t w4,
+                                                           uint32_t w5, uint32_t w6, uint32_t w7, float g) {
+  const uint32_t w[8] = {w0, w1, w2, w3, w4, w5, w6, w7};
+  float v[16];
+  widen16<T>(w, v);
+  BlockCodes r;
+  nvfp4_block<false>(v, g, kHiFirst, r.lo, r.hi, r.scale_byte);
+  return r;
+}
+
+template <typename T, bool kHiFirst>
+__device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const TensorScale& ts, uint32_t& lo_word,
+                                                   uint32_t& hi_word, uint32_t& scale_byte) {
+  static_assert(sizeof(T) == 2, "packed 16-bit inputs");
   const float amax = amax16_packed<T>(w);
   // Exactness window of the reciprocal-FMA quotients (all residuals representable): tensor
   // scale within 2^+-40, amax zero or within 2^+-60; then amax/6/g and every x/total below
@@ -209,6 +230,8 @@ __device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const
       const bool dead = (total == 0.0f);
       const float safe = dead ? 1.0f : total;
       const float y = __frcp_rn(safe);
+      float v[16];
+      widen16<T>(w, v);
       float q[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
@@ -226,7 +249,10 @@ __device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const
       return;
     }
   }
-  nvfp4_block<false>(v, ts.g, kHiFirst, lo_word, hi_word, scale_byte);
+  const BlockCodes r = nvfp4_block_packed_ieee<T, kHiFirst>(w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7], ts.g);
+  lo_word = r.lo;
+  hi_word = r.hi;
+  scale_byte = r.scale_byte;
 }
 
 }  // namespace quant
