@@ -273,9 +273,10 @@ __device__ __forceinline__ float round_to_out(float x) {
 // evaluated as x * sigmoid(2u) = x / (1 + 2^(-2u log2 e)) with the hardware exp2 and
 // reciprocal (relative error ~1e-6, far below the rounding of a 16-bit output type).
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float u = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+  // x * sigmoid(2u) = x / (1 + 2^(x * (k1 + k2 x^2))), k1 = -2 log2(e) sqrt(2/pi), k2 = 0.044715 k1
+  const float w = fmaf(-0.10294324f, x * x, -2.3022082f);
   float t, r;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(t) : "f"(-2.8853900817779268f * u));  // 2^(-2u log2 e) = e^(-2u)
+  asm("ex2.approx.f32 %0, %1;" : "=f"(t) : "f"(x * w));
   asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + t));
   return x * r;
 }
