@@ -212,42 +212,86 @@ __device__ __noinline__ BlockCodes nvfp4_block_packed_ieee(uint32_t w0, uint32_t
   return r;
 }
 
+// Codes of 16 exact quotients x / safe by the reciprocal-FMA chain (see div_markstein), out of
+// line: the streaming path below needs it only for blocks in which some quotient lies within
+// 2^-21 (relative) of an E2M1 rounding boundary.
+template <typename T, bool kHiFirst>
+__device__ __noinline__ uint2 nvfp4_codes_exact(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t w4,
+                                                uint32_t w5, uint32_t w6, uint32_t w7, float safe, float y) {
+  const uint32_t w[8] = {w0, w1, w2, w3, w4, w5, w6, w7};
+  float v[16], q[16];
+  widen16<T>(w, v);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
+  uint2 r;
+  if constexpr (kHiFirst) {
+    r.x = f32x8_to_e2m1_word(q[0], q[1], q[2], q[3], q[4], q[5], q[6], q[7]);
+    r.y = f32x8_to_e2m1_word(q[8], q[9], q[10], q[11], q[12], q[13], q[14], q[15]);
+  } else {
+    r.x = f32x8_to_e2m1_word(q[1], q[0], q[3], q[2], q[5], q[4], q[7], q[6]);
+    r.y = f32x8_to_e2m1_word(q[9], q[8], q[11], q[10], q[13], q[12], q[15], q[14]);
+  }
+  return r;
+}
+
+// 8 products v[i] * y -> one word of codes (nibble order as requested)
+template <bool kHiFirst>
+__device__ __forceinline__ uint32_t scaled_e2m1_word(const float* v, float y) {
+  if constexpr (kHiFirst) {
+    return f32x8_to_e2m1_word(v[0] * y, v[1] * y, v[2] * y, v[3] * y, v[4] * y, v[5] * y, v[6] * y, v[7] * y);
+  } else {
+    return f32x8_to_e2m1_word(v[1] * y, v[0] * y, v[3] * y, v[2] * y, v[5] * y, v[4] * y, v[7] * y, v[6] * y);
+  }
+}
+
+// The element quotients are not computed at all in the common case.  The code of x / total is
+// a monotone step function of the quotient, and RN(x / total) lies strictly between
+// x * y_lo and x * y_hi with y_lo = y (1 - 2^-21), y_hi = y (1 + 2^-21), y = RN(1 / total)
+// (the three roundings involved are below 2^-23 each, the quotient's own below 2^-24).  So
+// when both bracketing products convert to the same codes for a whole block - two multiplies
+// and one convert per element - those are the codes of the exact quotients; only a block in
+// which some product straddles a rounding boundary is redone with exact quotients.  A zero
+// keeps its sign through the multiplication, as the reference's cast keeps it.
 template <typename T, bool kHiFirst>
 __device__ __forceinline__ void nvfp4_block_packed(const uint32_t (&w)[8], const TensorScale& ts, uint32_t& lo_word,
                                                    uint32_t& hi_word, uint32_t& scale_byte) {
   static_assert(sizeof(T) == 2, "packed 16-bit inputs");
   const float amax = amax16_packed<T>(w);
-  // Exactness window of the reciprocal-FMA quotients (all residuals representable): tensor
-  // scale within 2^+-40, amax zero or within 2^+-60; then amax/6/g and every x/total below
-  // are normal numbers with normal residuals.  Anything else takes the IEEE-division path.
+  // Exactness window of the reciprocal-FMA quotients amax/6/g (all residuals representable):
+  // tensor scale within 2^+-40, amax zero or within 2^+-60; then total = g * scale is a normal
+  // number within 2^+-50 and its reciprocal is too.  Anything else takes the IEEE-division path.
   const bool fast_s = ts.in_window && (amax <= 0x1p60f) && (amax >= 0x1p-60f || amax == 0.0f);
   if (fast_s) {
     float s = div_markstein_nonneg(div_markstein_nonneg(amax, 6.0f, 0x1.555556p-3f /* RN(1/6) */), ts.g, ts.rcp);
     s = fminf(s, 448.0f);
     scale_byte = f32_to_e4m3_byte(s);
     const float total = __fmul_rn(ts.g, e4m3_byte_to_f32(scale_byte));
-    if (amax <= total * 0x1p20f) {  // also false for total == 0 with amax > 0
-      const bool dead = (total == 0.0f);
-      const float safe = dead ? 1.0f : total;
-      const float y = __frcp_rn(safe);
-      float v[16];
-      widen16<T>(w, v);
-      float q[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
-      if constexpr (kHiFirst) {
-        lo_word = f32x8_to_e2m1_word(q[0], q[1], q[2], q[3], q[4], q[5], q[6], q[7]);
-        hi_word = f32x8_to_e2m1_word(q[8], q[9], q[10], q[11], q[12], q[13], q[14], q[15]);
+    const bool dead = (total == 0.0f);
+    const float safe = dead ? 1.0f : total;
+    const float y = __frcp_rn(safe);
+    const float y_hi = __fmul_rn(y, 0x1.000008p0f), y_lo = __fmul_rn(y, 0x1.fffffp-1f);
+    float v[16];
+    widen16<T>(w, v);
+    lo_word = scaled_e2m1_word<kHiFirst>(v, y_hi);
+    hi_word = scaled_e2m1_word<kHiFirst>(v + 8, y_hi);
+    const uint32_t lo_b = scaled_e2m1_word<kHiFirst>(v, y_lo);
+    const uint32_t hi_b = scaled_e2m1_word<kHiFirst>(v + 8, y_lo);
+    if (((lo_word ^ lo_b) | (hi_word ^ hi_b)) != 0u) {
+      if (amax <= total * 0x1p20f) {  // residuals of the exact chain representable
+        const uint2 r = nvfp4_codes_exact<T, kHiFirst>(w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7], safe, y);
+        lo_word = r.x;
+        hi_word = r.y;
       } else {
-        lo_word = f32x8_to_e2m1_word(q[1], q[0], q[3], q[2], q[5], q[4], q[7], q[6]);
-        hi_word = f32x8_to_e2m1_word(q[9], q[8], q[11], q[10], q[13], q[12], q[15], q[14]);
+        const BlockCodes r = nvfp4_block_packed_ieee<T, kHiFirst>(w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7], ts.g);
+        lo_word = r.lo;
+        hi_word = r.hi;
       }
-      if (dead) {  // zero scale: every code is +0
-        lo_word = 0;
-        hi_word = 0;
-      }
-      return;
     }
+    if (dead) {  // zero scale: every code is +0
+      lo_word = 0;
+      hi_word = 0;
+    }
+    return;
   }
   const BlockCodes r = nvfp4_block_packed_ieee<T, kHiFirst>(w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7], ts.g);
   lo_word = r.lo;
