@@ -250,7 +250,28 @@ def make_steps(lib, wl: Workload, case: str):
                                     p(wl.out[j]), 2, rows, N, K, st)
         assert rc == 0, lib.ck_last_error()
 
+    dq4_bytes = rows * K // 2 + ((rows + 127) // 128 * 128) * (K // 16) + 4 + 2 * rows * K
+    dq8_bytes = rows * K + ((rows + 127) // 128 * 128) * (K // 32) + 2 * rows * K
+
+    def dq4(i, st):  # dequantizes what q4 of the same ring slot produced, into the x buffer of the next slot
+        j = i % wl.ring
+        rc = lib.ck_dequantize_nvfp4(p(wl.qx[j]), p(wl.sx), p(wl.bsx[j]), p(wl.deq[j]), 2, rows, K, 1, st)
+        assert rc == 0, lib.ck_last_error()
+
+    def dq8(i, st):
+        j = i % wl.ring
+        rc = lib.ck_dequantize_mxfp8(p(wl.qx8[j]), p(wl.bsx8[j]), p(wl.deq[j]), 2, rows, K, st)
+        assert rc == 0, lib.ck_last_error()
+
+    if case.startswith("dequantize"):
+        wl.deq = [wl.torch.empty(rows, K, dtype=wl.torch.bfloat16, device=wl.device) for _ in range(wl.ring)]
+        for j in range(wl.ring):  # operands of the timed kernel
+            (q4 if "nvfp4" in case else q8)(j, wl.torch.cuda.current_stream().cuda_stream)
+        wl.torch.cuda.synchronize()
+
     table = {
+        "dequantize_nvfp4": (dq4, 1, None, dq4_bytes),
+        "dequantize_mxfp8": (dq8, 1, None, dq8_bytes),
         "linear": (lambda i, st: (q4(i, st), g4(i, st)), 2, flops, None),
         "linear_mxfp8": (lambda i, st: (q8(i, st), g8(i, st)), 2, flops, None),
         "tensor_scale": (lambda i, st: _tensor_scale(lib, wl, i, st), 1, None, 2 * rows * K + 4),
@@ -758,7 +779,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="linear",
-                    choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
+                    choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "dequantize_nvfp4",
+                             "dequantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
                              "sharded_gemm", "mlp_pair", "mmdit"])
     ap.add_argument("--mmdit-blocks", default="", help="double,single block counts of --case mmdit (default 19,38)")
     ap.add_argument("--mmdit-batch", type=int, default=8, help="total batch of --case mmdit, split over the GPUs")

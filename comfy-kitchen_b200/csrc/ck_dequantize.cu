@@ -68,12 +68,24 @@ __device__ __forceinline__ float e4m3_byte_to_f32(uint32_t b) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xFFFFu)));
 }
 
+// Four packed bytes (eight E2M1 codes) -> four f16x2 pairs with the hardware convert; in each
+// pair the low half comes from the low nibble of its byte.  Every E2M1 value is exact in f16.
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t word, uint32_t (&h)[4]) {
+  asm("{ .reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3; }"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(word));
+}
+
 // one thread = one 16-element block of one row
-template <typename OutT>
+template <typename OutT, bool kHiFirst>
 __global__ void __launch_bounds__(kThreads)
 dequantize_nvfp4_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ global_scale,
-                        const uint8_t* __restrict__ scales, OutT* __restrict__ out, int64_t rows, int64_t cols,
-                        int hi_first) {
+                        const uint8_t* __restrict__ scales, OutT* __restrict__ out, int64_t rows, int64_t cols) {
   const int64_t n_sc = cols >> 4;
   const int64_t sc = static_cast<int64_t>(blockIdx.y) * 64 + threadIdx.x;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + threadIdx.y;
@@ -86,11 +98,16 @@ dequantize_nvfp4_kernel(const uint8_t* __restrict__ codes, const float* __restri
   const float total = round_to<OutT>(ts * bs);
   float v[16];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t byte = ((i < 4 ? packed.x : packed.y) >> (8 * (i & 3))) & 0xFFu;
-    const uint32_t hi = byte >> 4, lo = byte & 0xFu;
-    v[2 * i] = e2m1_value(hi_first ? hi : lo) * total;      // :214, rounded by the store
-    v[2 * i + 1] = e2m1_value(hi_first ? lo : hi) * total;
+  for (int w = 0; w < 2; ++w) {
+    uint32_t h[4];
+    e2m1x8_to_f16x2(w == 0 ? packed.x : packed.y, h);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));  // (low nibble, high nibble)
+      // :214, rounded by the store; the product of two OutT numbers is exact in float32
+      v[8 * w + 2 * i] = (kHiFirst ? f.y : f.x) * total;
+      v[8 * w + 2 * i + 1] = (kHiFirst ? f.x : f.y) * total;
+    }
   }
   store16<OutT>(out + row * cols + sc * 16, v);
 }
@@ -148,11 +165,14 @@ extern "C" int ck_dequantize_nvfp4(const void* codes, const float* global_scale,
   const uint8_t* c = static_cast<const uint8_t*>(codes);
   const uint8_t* sc = static_cast<const uint8_t*>(block_scales);
   if (out_dtype == CK_DTYPE_BF16) {
-    dequantize_nvfp4_kernel<<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<__nv_bfloat16*>(out), rows, cols, hi_first);
+    if (hi_first) dequantize_nvfp4_kernel<__nv_bfloat16, true><<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<__nv_bfloat16*>(out), rows, cols);
+    else dequantize_nvfp4_kernel<__nv_bfloat16, false><<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<__nv_bfloat16*>(out), rows, cols);
   } else if (out_dtype == CK_DTYPE_F16) {
-    dequantize_nvfp4_kernel<<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<__half*>(out), rows, cols, hi_first);
+    if (hi_first) dequantize_nvfp4_kernel<__half, true><<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<__half*>(out), rows, cols);
+    else dequantize_nvfp4_kernel<__half, false><<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<__half*>(out), rows, cols);
   } else {
-    dequantize_nvfp4_kernel<<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<float*>(out), rows, cols, hi_first);
+    if (hi_first) dequantize_nvfp4_kernel<float, true><<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<float*>(out), rows, cols);
+    else dequantize_nvfp4_kernel<float, false><<<grid, block, 0, s>>>(c, global_scale, sc, static_cast<float*>(out), rows, cols);
   }
   CK_CUDA(cudaGetLastError());
   return CK_OK;

@@ -135,7 +135,10 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
 #ifndef CK_Q_MINBLOCKS
 #define CK_Q_MINBLOCKS 4
 #endif
-constexpr int kPairRows = 8;  // rows per thread block; 32 lanes x 2 blocks x 16 = 1024 columns per warp
+#ifndef CK_Q_ROWS
+#define CK_Q_ROWS 8
+#endif
+constexpr int kPairRows = CK_Q_ROWS;  // rows per thread block; 32 lanes x 2 blocks x 16 = 1024 columns per warp
 
 template <typename T, bool kHiFirst>
 __global__ void __launch_bounds__(32 * kPairRows, CK_Q_MINBLOCKS)
