@@ -714,7 +714,7 @@ def run_gpu_arm(args) -> dict | None:
     # to the rows: per-row figures); the GEMMs at the 4096-row workload itself (operand reads; the
     # output is still in L2 when the kernel ends).
     def ncu_traffic(kernel):
-        per_row = {"quantize_nvfp4": (201.615872e6 + 39.962880e6) / 32768, "quantize_mxfp8": (201.338880e6 + 74.617600e6) / 32768}
+        per_row = {"quantize_nvfp4": (201.498368e6 + 40.577536e6) / 32768, "dequantize_nvfp4": (56.629504e6 + 143.971584e6) / 32768, "quantize_mxfp8": (201.338880e6 + 74.617600e6) / 32768}
         fixed_4096 = {"scaled_mm_nvfp4": 12.437248e6 + 1.536e3, "scaled_mm_mxfp8": 22.758144e6 + 81.664e3}
         key = kernel.replace("gemm_", "scaled_mm_")
         if key in per_row:
