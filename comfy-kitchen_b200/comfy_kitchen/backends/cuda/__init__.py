@@ -50,6 +50,9 @@ _SIGNATURES = {
     "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_gemm_status": [_P],
+    "ck_scaled_mm_workspace_bytes": [_I, _L, _L, _L],
+    "ck_scaled_mm_nvfp4_ws": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
+    "ck_scaled_mm_mxfp8_ws": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
     "ck_nvfp4_tensor_scale_scratch_bytes": [_L],
     "ck_nvfp4_tensor_scale": [_P, _I, _L, _P, _P, _L, _P],
     "ck_nvfp4_tensor_scale_noalloc": [_P, _I, _L, _P, _P],
@@ -62,7 +65,8 @@ _SIGNATURES = {
     "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],
     "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
 }
-_RESTYPE = {"ck_last_error": ctypes.c_char_p, "ck_nvfp4_tensor_scale_scratch_bytes": ctypes.c_int64}
+_RESTYPE = {"ck_last_error": ctypes.c_char_p, "ck_nvfp4_tensor_scale_scratch_bytes": ctypes.c_int64,
+            "ck_scaled_mm_workspace_bytes": ctypes.c_int64}
 
 
 def library_path() -> str:
@@ -281,11 +285,34 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
     bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        _check(lib.ck_scaled_mm_nvfp4(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa), _ptr(tsb),
-                                      _ptr(alpha_t), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
-                                      _stream(dev)), "scaled_mm_nvfp4")
+        ws_ptr, ws_bytes = _gemm_workspace(lib, False, m, n, k, dev)
+        _check(lib.ck_scaled_mm_nvfp4_ws(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa), _ptr(tsb),
+                                         _ptr(alpha_t), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
+                                         ws_ptr, ws_bytes, _stream(dev)), "scaled_mm_nvfp4")
     del bias_keep
     return out
+
+
+_gemm_workspaces: dict = {}
+_retired_workspaces: list = []  # outgrown buffers stay alive: a captured CUDA graph may still point at them
+
+
+def _gemm_workspace(lib, is_mxfp8: bool, m: int, n: int, k: int, device):
+    """(pointer, bytes) of the split-K workspace for this shape on the current stream, or (None, 0).
+
+    The library decides (few output tiles, long K); the buffer is cached per device and stream
+    and only ever grows, so steady-state calls allocate nothing."""
+    need = int(lib.ck_scaled_mm_workspace_bytes(int(is_mxfp8), m, n, k))
+    if need == 0:
+        return None, 0
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _gemm_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _gemm_workspaces[key] = ws
+    return ws.data_ptr(), ws.numel()
 
 
 def _pointer_array(ptrs):
@@ -425,8 +452,10 @@ def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
     bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        _check(lib.ck_scaled_mm_mxfp8(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), bias_ptr, bias_code,
-                                      _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, _stream(dev)), "scaled_mm_mxfp8")
+        ws_ptr, ws_bytes = _gemm_workspace(lib, True, m, n, k, dev)
+        _check(lib.ck_scaled_mm_mxfp8_ws(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), bias_ptr, bias_code,
+                                         _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, ws_ptr, ws_bytes, _stream(dev)),
+               "scaled_mm_mxfp8")
     del bias_keep
     return out
 

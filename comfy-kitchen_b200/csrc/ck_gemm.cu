@@ -125,6 +125,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int out_tma;             // the output qualifies for TMA stores (16-byte aligned base and pitch)
   int n_out;               // destinations of every output tile (1, or one per GPU of an all-gather)
+  int splits;              // split-K: work items per tile (1 = off); item s of a tile covers pipeline stages
+  int k_stages_per_split;  //   [s * k_stages_per_split, ...) and stores its raw fp32 partial to destination s
   int* status;             // device status word: set non-zero when a wait gave up
   // fused epilogue (FUSED kernels only)
   int activation;          // CK_ACT_*
@@ -351,6 +353,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   pdl_wait();
 
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const int splits = p.splits;
+  const int num_items = num_tiles * splits;
   const int k_stages = (p.k_bytes + kStageKBytes - 1) / kStageKBytes;
   const int total_mma = (p.k_bytes + kMmaKBytes - 1) / kMmaKBytes;
 
@@ -362,7 +366,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     int ring_s = 0;
     uint32_t ring_ph = 0;
     [[maybe_unused]] uint32_t tile_it = 0;
-    for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
+    for (int item = worker; item < num_items; item += num_workers, ++tile_it) {
+      const int tile = item / splits;
+      const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
+      const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
       // consecutive workers take tiles that share the B columns (tile_m fastest)
       const int tile_m = tile % p.tiles_m;
       const int tile_n = tile / p.tiles_m;
@@ -376,7 +383,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const bool have_sfa = (m0 / kTileM) < p.n_row_blocks_a;
       const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(m0 / kTileM) * p.sf_col_tiles * 512;
       const uint8_t* sfb_src = p.sfb + static_cast<int64_t>(rb_b0) * p.sf_col_tiles * 512;
-      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+      for (int ks = ks_begin; ks < ks_end; ++ks, ++it) {
         // ring position and phase as running counters (STAGES is not a power of two)
         const int s = ring_s;
         const uint32_t ph = ring_ph;
@@ -389,8 +396,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         } else {
           mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
         }
-        if (ks == 0) CK_TRACE(4);
-        if (ks == k_stages - 1) CK_TRACE(5);
+        if (ks == ks_begin) CK_TRACE(4);
+        if (ks == ks_end - 1) CK_TRACE(5);
         CK_TRACE2(0, it);
         if constexpr (CTAS == 2) {
           // Every load of both CTAs reports its bytes to the leader's barrier; scale tiles
@@ -456,14 +463,17 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint32_t ring_ph = 0;
     uint32_t sf_ring = 0;
     uint32_t tile_it = 0;
-    for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
+    for (int item = worker; item < num_items; item += num_workers, ++tile_it) {
+      const int tile = item / splits;
+      const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
+      const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
       const int n0 = (tile / p.tiles_m) * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
       // B scale words of this tile start (n0 % 128) / 32 columns into the first row block
       const uint32_t sfb_shift = (n0 % 128) / 32;
-      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+      for (int ks = ks_begin; ks < ks_end; ++ks, ++it) {
         const int s = ring_s;
         const uint32_t ph = ring_ph;
         if (++ring_s == STAGES) {
@@ -478,8 +488,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         } else {
           mbar_wait(&full_bar[s], ph, abort_flag);
         }
-        if (ks == 0) CK_TRACE(2);
-        if (ks == k_stages - 1) CK_TRACE(3);
+        if (ks == ks_begin) CK_TRACE(2);
+        if (ks == ks_end - 1) CK_TRACE(3);
         CK_TRACE2(2, it);
 #ifdef CK_GEMM_TRACE
         if (tile_it == 1 && ks < kTraceSlots && lane == 0 && blockIdx.x < 160)
@@ -505,7 +515,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                            desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
             }
           }
-          if (ks == 0) {
+          if (ks == ks_begin) {
             // Only now does the tile need its accumulator: the wait for the epilogue to have
             // drained it comes after the first stage's operands have landed and its scale
             // copies are issued, which takes those steps off the tile-to-tile critical path.
@@ -517,7 +527,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
           for (int kb = 0; kb < kMmaPerStage; ++kb) {
             if (kb < n_mma) {
-              const uint32_t accumulate = (ks | kb) != 0 ? 1u : 0u;
+              const uint32_t accumulate = (ks != ks_begin || kb != 0) ? 1u : 0u;
               // advancing K inside the swizzle atom = advancing the start address (32 B = 2 units)
               const uint64_t a_desc = desc64(a_lo + kb * 2, op_hi);
               const uint64_t b_desc = desc64(b_lo + kb * 2, op_hi);
@@ -538,7 +548,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #endif
           tc_commit<CTAS>(empty_addr + s * 8);
           if constexpr (CTAS == 2) tc_commit<CTAS>(empty_addr_peer + s * 8);
-          if (ks == k_stages - 1) {
+          if (ks == ks_end - 1) {
             tc_commit<CTAS>(acc_full_addr + acc * 8);
             if constexpr (CTAS == 2) tc_commit<CTAS>(acc_full_addr_peer + acc * 8);
           }
@@ -571,7 +581,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t acc_empty_leader = (CTAS == 2) ? map_to_cta(smem_u32(acc_empty_bar), 0) : 0u;
     [[maybe_unused]] uint32_t out_box = 0;  // boxes this warp has staged so far (ring index)
     uint32_t tile_it = 0;
-    for (int tile = worker; tile < num_tiles; tile += num_workers, ++tile_it) {
+    for (int item = worker; item < num_items; item += num_workers, ++tile_it) {
+      const int tile = item / splits;
+      const int split = item - tile * splits;
       const int tile_m = tile % p.tiles_m;
       const int tile_n = tile / p.tiles_m;
       const int row = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM + quarter * 32 + lane;
@@ -582,7 +594,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       float* bias_s = smem_bias + (tile_it & 1) * TILE_N;
       for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
         const int n = n0 + c;
-        bias_s[c] = (p.bias != nullptr && n < p.N) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
+        bias_s[c] = (p.bias != nullptr && n < p.N && splits == 1) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
       if (warp == 2) CK_TRACE(6);
@@ -667,8 +679,12 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #else
                 if (lane == 0 && row0 < p.M && col < p.N) {
 #endif
-                  // the same staged box goes to every destination (peer stores cross NVLink)
-                  for (int d = 0; d < p.n_out; ++d) tma_store_2d_addr(&maps_out.m[d], stage_box, col, row0);
+                  if (splits > 1) {
+                    tma_store_2d_addr(&maps_out.m[split], stage_box, col, row0);  // this item's partial
+                  } else {
+                    // the same staged box goes to every destination (peer stores cross NVLink)
+                    for (int d = 0; d < p.n_out; ++d) tma_store_2d_addr(&maps_out.m[d], stage_box, col, row0);
+                  }
                 }
                 // (an empty group when nothing was stored keeps the ring's group count in step)
                 if (lane == 0) bulk_commit_group();
@@ -962,7 +978,7 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
     }
     if (dev >= 0 && dev < 64) max_workers[dev].store(resident, std::memory_order_release);
   }
-  int workers = min(p.tiles_m * p.tiles_n, resident);
+  int workers = min(p.tiles_m * p.tiles_n * p.splits, resident);
 #ifdef CK_GEMM_TRACE
   if (const char* e = getenv("CK_GEMM_MAX_WORKERS")) workers = min(workers, atoi(e));
 #endif
@@ -1049,6 +1065,92 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[5], co
   }
 }
 
+// ---------------------------------------------------------------------------
+// split-K
+// ---------------------------------------------------------------------------
+struct SplitPlan {
+  int splits;
+  int k_stages_per_split;
+};
+
+// More than one split only when the 128 x 128 tiles leave at least half of the SMs idle and K is
+// long enough (>= 16 pipeline stages) for the extra pass over the partial tiles to pay.
+SplitPlan plan_splits(int64_t M, int64_t N, int k_bytes) {
+  const int k_stages = static_cast<int>(ceil_div(k_bytes, kStageKBytes));
+  const int64_t tiles = ceil_div(M, kTileM) * ceil_div(N, 128);
+  SplitPlan plan = {1, k_stages};
+  if (tiles * 2 > sm_count() || k_stages < 16) return plan;
+  const int64_t by_sms = sm_count() / tiles;
+  int splits = min(kMaxOutputs, k_stages / 6);
+  if (by_sms < splits) splits = static_cast<int>(by_sms);
+  if (splits < 2) return plan;
+  plan.k_stages_per_split = static_cast<int>(ceil_div(k_stages, splits));
+  plan.splits = static_cast<int>(ceil_div(k_stages, plan.k_stages_per_split));
+  return plan;
+}
+
+// out = cast(alpha * (partial_0 + partial_1 + ...) + bias), four consecutive columns per thread;
+// the partials are added in index order, so the result does not depend on scheduling.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partials, int splits, int64_t mn, int n_cols, const float* __restrict__ alpha_ptr,
+                     const float* __restrict__ tsa, const float* __restrict__ tsb, const void* __restrict__ bias,
+                     int bias_dtype, OutT* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= mn) return;
+  float alpha = 1.0f;
+  if (alpha_ptr != nullptr) {
+    alpha = __ldg(alpha_ptr);
+  } else if (tsa != nullptr && tsb != nullptr) {
+    alpha = __ldg(tsa) * __ldg(tsb);
+  }
+  float4 acc = *reinterpret_cast<const float4*>(partials + i);
+  for (int sidx = 1; sidx < splits; ++sidx) {
+    const float4 v = *reinterpret_cast<const float4*>(partials + sidx * mn + i);
+    acc.x += v.x;
+    acc.y += v.y;
+    acc.z += v.z;
+    acc.w += v.w;
+  }
+  const int n = static_cast<int>(i % n_cols);
+  float b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = load_bias(bias, bias_dtype, n + j);
+  }
+  const float r[4] = {fmaf(acc.x, alpha, b[0]), fmaf(acc.y, alpha, b[1]), fmaf(acc.z, alpha, b[2]), fmaf(acc.w, alpha, b[3])};
+  if constexpr (std::is_same<OutT, float>::value) {
+    *reinterpret_cast<float4*>(out + i) = make_float4(r[0], r[1], r[2], r[3]);
+  } else {
+    uint2 o;
+    o.x = pack_pair<OutT>(r[0], r[1]);
+    o.y = pack_pair<OutT>(r[2], r[3]);
+    *reinterpret_cast<uint2*>(out + i) = o;
+  }
+}
+
+int launch_splitk_reduce(const float* partials, int splits, int64_t M, int64_t N, const GemmParams& p, cudaStream_t stream) {
+  const int64_t mn = M * N;
+  const dim3 grid(static_cast<unsigned>(ceil_div(mn / 4, 256))), block(256);
+  const int n_cols = static_cast<int>(N);
+  switch (p.out_dtype) {
+    case CK_DTYPE_BF16:
+      CK_CUDA(launch_pdl(splitk_reduce_kernel<__nv_bfloat16>, grid, block, 0, stream, partials, splits, mn, n_cols, p.alpha, p.tsa,
+                         p.tsb, p.bias, p.bias_dtype, static_cast<__nv_bfloat16*>(p.out)));
+      break;
+    case CK_DTYPE_F16:
+      CK_CUDA(launch_pdl(splitk_reduce_kernel<__half>, grid, block, 0, stream, partials, splits, mn, n_cols, p.alpha, p.tsa, p.tsb,
+                         p.bias, p.bias_dtype, static_cast<__half*>(p.out)));
+      break;
+    default:
+      CK_CUDA(launch_pdl(splitk_reduce_kernel<float>, grid, block, 0, stream, partials, splits, mn, n_cols, p.alpha, p.tsa, p.tsb,
+                         p.bias, p.bias_dtype, static_cast<float*>(p.out)));
+  }
+  return CK_OK;
+}
+
 struct FusedArgs {
   bool enabled = false;
   int activation = CK_ACT_NONE;
@@ -1061,7 +1163,7 @@ template <Kind KIND>
 int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, const void* sfb, const float* tsa,
               const float* tsb, const float* alpha, const void* bias, int bias_dtype, void* out, int out_dtype,
               int64_t M, int64_t N, int64_t K, void* stream, const FusedArgs& fused = FusedArgs(),
-              const OutputSpec* out_spec = nullptr) {
+              const OutputSpec* out_spec = nullptr, void* workspace = nullptr, int64_t workspace_bytes = 0) {
   CK_REQUIRE(a && b && sfa && sfb, "%s: null pointer", op);
   CK_REQUIRE(out != nullptr || (fused.enabled && fused.rq_codes != nullptr), "%s: no output requested", op);
   if (fused.enabled) {
@@ -1111,6 +1213,8 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.rq_scale = fused.rq_scale;
   p.n_row_blocks_a = static_cast<int>(ceil_div(M, 128));
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
+  p.splits = 1;
+  p.k_stages_per_split = static_cast<int>(ceil_div(p.k_bytes, kStageKBytes));
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
 
   CUtensorMap map_a, map_b[5];
@@ -1134,6 +1238,31 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
     os.n = 1;
     os.pitch = N;
     os.col_offset = 0;
+  }
+  // Split-K for problems with few tiles and a long K (small M): the tiles' K ranges are spread
+  // over otherwise idle SMs as separate work items that store raw fp32 partial tiles to the
+  // caller's workspace; a second kernel adds them in a fixed order and applies alpha and bias.
+  if (workspace != nullptr && !fused.enabled && out_spec == nullptr && forced_config() == 0) {
+    const SplitPlan plan = plan_splits(M, N, p.k_bytes);
+    const int64_t need = static_cast<int64_t>(plan.splits) * M * N * 4;
+    if (plan.splits > 1 && workspace_bytes >= need && reinterpret_cast<uintptr_t>(workspace) % 16 == 0 && (N * 4) % 16 == 0) {
+      GemmParams ps = p;
+      ps.tsa = ps.tsb = ps.alpha = nullptr;
+      ps.bias = nullptr;
+      ps.out = workspace;
+      ps.out_dtype = CK_DTYPE_F32;
+      ps.splits = plan.splits;
+      ps.k_stages_per_split = plan.k_stages_per_split;
+      void* parts[kMaxOutputs] = {};
+      for (int i = 0; i < plan.splits; ++i) parts[i] = static_cast<uint8_t*>(workspace) + static_cast<int64_t>(i) * M * N * 4;
+      OutputSpec ws_spec;
+      ws_spec.ptrs = parts;
+      ws_spec.n = plan.splits;
+      ws_spec.pitch = N;
+      ws_spec.col_offset = 0;
+      if (int rc = launch_config<KIND, 128, 2, 5, 1, float, false, 1>(map_a, map_b[0], ps, ws_spec, s)) return rc;
+      return launch_splitk_reduce(static_cast<const float*>(workspace), plan.splits, M, N, p, s);
+    }
   }
   if constexpr (KIND == Kind::kNvfp4) {
     if (fused.enabled) {
@@ -1188,6 +1317,29 @@ extern "C" int ck_linear_nvfp4_fused(const void* a, const void* b, const void* s
   f.rq_scale = requant_scale;
   return ck::scaled_mm<ck::Kind::kNvfp4>("linear_nvfp4_fused", a, b, sfa, sfb, tensor_scale_a, tensor_scale_b, alpha, bias,
                                          bias_dtype, out, out_dtype, M, N, K, stream, f);
+}
+
+extern "C" int64_t ck_scaled_mm_workspace_bytes(int is_mxfp8, int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || M >= (1ll << 30) || N >= (1ll << 30) || K >= (1ll << 30)) return 0;
+  const ck::SplitPlan plan = ck::plan_splits(M, N, static_cast<int>(is_mxfp8 ? K : K / 2));
+  return plan.splits > 1 ? static_cast<int64_t>(plan.splits) * M * N * 4 : 0;
+}
+
+extern "C" int ck_scaled_mm_nvfp4_ws(const void* a, const void* b, const void* sfa, const void* sfb,
+                                     const float* tensor_scale_a, const float* tensor_scale_b, const float* alpha,
+                                     const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                                     int64_t K, void* workspace, int64_t workspace_bytes, void* stream) {
+  return ck::scaled_mm<ck::Kind::kNvfp4>("scaled_mm_nvfp4", a, b, sfa, sfb, tensor_scale_a, tensor_scale_b, alpha, bias,
+                                         bias_dtype, out, out_dtype, M, N, K, stream, ck::FusedArgs(), nullptr, workspace,
+                                         workspace_bytes);
+}
+
+extern "C" int ck_scaled_mm_mxfp8_ws(const void* a, const void* b, const void* sfa, const void* sfb, const void* bias,
+                                     int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                                     void* workspace, int64_t workspace_bytes, void* stream) {
+  return ck::scaled_mm<ck::Kind::kMxfp8>("scaled_mm_mxfp8", a, b, sfa, sfb, nullptr, nullptr, nullptr, bias, bias_dtype,
+                                         out, out_dtype, M, N, K, stream, ck::FusedArgs(), nullptr, workspace,
+                                         workspace_bytes);
 }
 
 extern "C" int ck_scaled_mm_nvfp4_allgather(const void* a, const void* b, const void* sfa, const void* sfb,

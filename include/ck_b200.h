@@ -210,6 +210,27 @@ CK_API int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa, con
                        void* out, int out_dtype,
                        int64_t M, int64_t N, int64_t K, void* stream);
 
+/*
+ * Variants of the two GEMMs that may use a caller-owned workspace (the reference hands its
+ * cuBLASLt call a workspace the same way, comfy_kitchen/backends/cuda/__init__.py:117-124,
+ * ops/cublas_gemm_nvfp4.cu:297-311).  ck_scaled_mm_workspace_bytes says how many bytes the
+ * library would use for this shape: non-zero only for problems with few output tiles and a long
+ * K (small M), which are then computed split-K - partial fp32 tiles in the workspace, a second
+ * kernel adds them in a fixed order (deterministic) and applies alpha and bias.  With a null or
+ * too small workspace the calls behave exactly like ck_scaled_mm_nvfp4 / ck_scaled_mm_mxfp8.
+ * The workspace must be 16-byte aligned and must not be shared by calls that can overlap.
+ */
+CK_API int64_t ck_scaled_mm_workspace_bytes(int is_mxfp8, int64_t M, int64_t N, int64_t K);
+CK_API int ck_scaled_mm_nvfp4_ws(const void* a, const void* b, const void* block_scale_a,
+                          const void* block_scale_b, const float* tensor_scale_a,
+                          const float* tensor_scale_b, const float* alpha, const void* bias,
+                          int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                          void* workspace, int64_t workspace_bytes, void* stream);
+CK_API int ck_scaled_mm_mxfp8_ws(const void* a, const void* b, const void* block_scale_a,
+                          const void* block_scale_b, const void* bias, int bias_dtype, void* out,
+                          int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace,
+                          int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------ multi-GPU (one node) */
 /*
  * Column-sharded GEMM with the all-gather of the output fused into the epilogue.  No

@@ -203,3 +203,21 @@ def test_gemm_is_deterministic_and_row_independent(ck, cuda_device):
     o_top = ck.scaled_mm_nvfp4(qa_top, qb, sa, sb, bsa_top, bsb, bias=bias.to(dev))
     assert gemm_status() == 0
     assert torch.equal(o_top, o1[:256])
+
+
+@pytest.mark.parametrize("shape", [(16, 3072, 12288), (256, 3072, 12288), (1, 1024, 8192), (130, 640, 4096), (48, 136, 6144)])
+def test_split_k_for_small_m_long_k(ck, cuda_device, shape):
+    """Few output tiles and a long K: the public call computes split-K through its cached workspace
+    (the library reports a non-zero workspace size for these shapes) and still meets the GEMM
+    contract, deterministically."""
+    from comfy_kitchen.backends import cuda as backend
+
+    m, n, k = shape
+    lib = backend.load_library()
+    assert lib.ck_scaled_mm_workspace_bytes(0, m, n, k) > 0
+    assert lib.ck_scaled_mm_workspace_bytes(0, 4096, 3072, 3072) == 0
+    a, b, bias = _operands(m, n, k, seed=m + n + k)
+    _check_nvfp4(ck, cuda_device, a, b, bias, torch.bfloat16)
+    _check_nvfp4(ck, cuda_device, a, b, None, torch.float32)
+    _check_mxfp8(ck, cuda_device, a, b, bias, torch.bfloat16)
+    assert gemm_status() == 0
