@@ -84,7 +84,7 @@ struct Config {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kOutStageBytes = OUT_STAGE * epilogue_warps(false, TILE_N, CTAS) * 4096;
   static constexpr int kRingBytes = (STAGES * kStageBytes + 1023) / 1024 * 1024;
-  static constexpr int kSmemBytes = kRingBytes + kOutStageBytes + 2 * TILE_N * 4 /*bias*/ +
+  static constexpr int kSmemBytes = kRingBytes + kOutStageBytes + 3 * TILE_N * 4 /*bias*/ +
                                     1024 /*alignment slack*/ + 256 /*barriers*/;
   // tensor memory columns
   static constexpr int kAccCols = TILE_N;
@@ -312,8 +312,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem_sfa = smem_b + STAGES * Cfg::kBBytes;
   uint8_t* smem_sfb = smem_sfa + STAGES * Cfg::kSfaBytes;
   uint8_t* smem_out = smem + Cfg::kRingBytes;  // 1024-byte aligned (swizzled store boxes)
-  float* smem_bias = reinterpret_cast<float*>(smem_out + Cfg::kOutStageBytes);  // [2][TILE_N]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bias + 2 * TILE_N);
+  float* smem_bias = reinterpret_cast<float*>(smem_out + Cfg::kOutStageBytes);  // [3][TILE_N]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bias + 3 * TILE_N);
   uint64_t* full_bar = bars;                       // [STAGES] producer -> MMA
   uint64_t* empty_bar = bars + STAGES;             // [STAGES] MMA -> producer
   uint64_t* acc_full_bar = bars + 2 * STAGES;      // [NUM_ACC] MMA -> epilogue
@@ -590,13 +590,19 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int n0 = tile_n * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
-      // bias of this tile's columns as fp32 in shared memory (double-buffered across tiles)
-      float* bias_s = smem_bias + (tile_it & 1) * TILE_N;
-      for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
-        const int n = n0 + c;
-        bias_s[c] = (p.bias != nullptr && n < p.N && splits == 1) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
+      // Bias of a tile's columns as fp32 in shared memory, three buffers in rotation: the
+      // buffer of tile t is filled while tile t - 1 is in its epilogue (right after the drain,
+      // where the warps are aligned anyway), so no barrier stands between the end of one
+      // epilogue and the wait for the next accumulator.  A warp can run at most one tile ahead
+      // of the slowest one (the barrier below), hence the third buffer.
+      float* bias_s = smem_bias + (tile_it % 3) * TILE_N;
+      if (tile_it == 0) {
+        for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
+          const int n = n0 + c;
+          bias_s[c] = (p.bias != nullptr && n < p.N && splits == 1) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
       if (warp == 2) CK_TRACE(6);
       if constexpr (CTAS == 2) {
         mbar_wait_cluster(&acc_full_bar[acc], acc_ph, abort_flag);
@@ -607,10 +613,30 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc_fence_after_sync();
       const int c0 = half * kColsPerWarp;
       const uint32_t t_row = tmem_base + acc * Cfg::kAccCols + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
-      uint32_t buf[kChunks][32];
+      // The fused 16-bit epilogue never holds the raw accumulator: it drains 32 columns at a
+      // time and keeps alpha * acc + bias rounded to OutT as packed pairs (a quarter of the
+      // registers); the others pull their whole share with back-to-back loads.
+      constexpr bool kPackedDrain = FUSED && sizeof(OutT) == 2;
+      uint32_t buf[kPackedDrain ? 1 : kChunks][32];
+      [[maybe_unused]] uint32_t pk[kPackedDrain ? kChunks : 1][16];
+      if constexpr (kPackedDrain) {
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) tmem_load_32x32(t_row + c * 32, buf[c]);
-      tmem_load_wait();
+        for (int c = 0; c < kChunks; ++c) {
+          tmem_load_32x32(t_row + c * 32, buf[0]);
+          tmem_load_wait();
+          const float2* b2 = reinterpret_cast<const float2*>(bias_s + c0 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 b = b2[i];
+            pk[c][i] = pack_pair<OutT>(fmaf(__uint_as_float(buf[0][2 * i]), alpha, b.x),
+                                       fmaf(__uint_as_float(buf[0][2 * i + 1]), alpha, b.y));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) tmem_load_32x32(t_row + c * 32, buf[c]);
+        tmem_load_wait();
+      }
       if (warp == 2) CK_TRACE(8);
       tc_fence_before_sync();
       __syncwarp();
@@ -619,6 +645,18 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           mbar_arrive_cluster(acc_empty_leader + acc * 8);  // the leader's barrier counts both CTAs' warps
         } else {
           mbar_arrive(&acc_empty_bar[acc]);
+        }
+      }
+      {
+        const int next_item = item + num_workers;
+        if (next_item < num_items) {
+          float* bias_next = smem_bias + ((tile_it + 1) % 3) * TILE_N;
+          const int next_n0 = ((next_item / splits) / p.tiles_m) * TILE_N;
+          for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
+            const int n = next_n0 + c;
+            bias_next[c] = (p.bias != nullptr && n < p.N && splits == 1) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
         }
       }
       OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0 + c0;
@@ -711,76 +749,64 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int rq_col_tiles = (p.N / 16 + 3) / 4;
         const int rows_pad = (p.M + 127) / 128 * 128;
         uint32_t scale_word = 0;
-        bool packed_path = false;
-        if constexpr (sizeof(OutT) == 2) packed_path = (n0 + c0 + kColsPerWarp <= p.N);
-        if (packed_path) {
-          if constexpr (sizeof(OutT) == 2) {
-            // 16-bit outputs, whole chunks: the values an unfused caller would see are the
-            // accumulators rounded to OutT, so they are kept as packed pairs from here on (half
-            // the registers), the activation works pair by pair, and the re-quantization runs on
-            // the packed words exactly as the stand-alone quantizer does.
-            const quant::TensorScale rq_ts = quant::make_tensor_scale(rq_g);
-            uint32_t pk[kChunks][16];
-            if (row < p.M) {
+        if constexpr (kPackedDrain) {
+          // The values an unfused caller would see are the accumulators rounded to OutT: the
+          // activation works on the packed pairs, and the re-quantization runs on the packed
+          // words exactly as the stand-alone quantizer does.
+          const quant::TensorScale rq_ts = quant::make_tensor_scale(rq_g);
 #pragma unroll
-              for (int c = 0; c < kChunks; ++c) {
-                const float2* b2 = reinterpret_cast<const float2*>(bias_s + c0 + c * 32);
+          for (int c = 0; c < kChunks; ++c) {
+            const int col = n0 + c0 + c * 32;
+            const int valid = min(32, p.N - col);
+            if (valid <= 0) continue;
+            if (row < p.M) {
+              if (p.activation == CK_ACT_GELU_TANH) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                  const float2 b = b2[i];
-                  pk[c][i] = pack_pair<OutT>(fmaf(__uint_as_float(buf[c][2 * i]), alpha, b.x),
-                                             fmaf(__uint_as_float(buf[c][2 * i + 1]), alpha, b.y));
+                  float a, b;
+                  unpack_pair<OutT>(pk[c][i], a, b);
+                  pk[c][i] = pack_pair<OutT>(gelu_tanh(a), gelu_tanh(b));
+                }
+              }
+              if (p.out != nullptr) {
+                if (vec_ok && valid == 32) {
+                  Vec256 o0, o1;
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    o0.w[i] = pk[c][i];
+                    o1.w[i] = pk[c][8 + i];
+                  }
+                  st_global_256(out_row + c * 32, o0);
+                  st_global_256(out_row + c * 32 + 16, o1);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) {  // N % 8 == 0: pairs never straddle the edge
+                    if (2 * i < valid) *reinterpret_cast<uint32_t*>(out_row + c * 32 + 2 * i) = pk[c][i];
+                  }
                 }
               }
             }
-#pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-              const int col = n0 + c0 + c * 32;
+            if (p.rq_codes != nullptr) {  // N % 64 == 0 here: every chunk is whole
               if (row < p.M) {
-                if (p.activation == CK_ACT_GELU_TANH) {
+                uint32_t lo[8], hi[8];
 #pragma unroll
-                  for (int i = 0; i < 16; ++i) {
-                    float a, b;
-                    unpack_pair<OutT>(pk[c][i], a, b);
-                    pk[c][i] = pack_pair<OutT>(gelu_tanh(a), gelu_tanh(b));
-                  }
+                for (int i = 0; i < 8; ++i) {
+                  lo[i] = pk[c][i];
+                  hi[i] = pk[c][8 + i];
                 }
-                if (p.out != nullptr) {
-                  if (vec_ok) {
-                    Vec256 o0, o1;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                      o0.w[i] = pk[c][i];
-                      o1.w[i] = pk[c][8 + i];
-                    }
-                    st_global_256(out_row + c * 32, o0);
-                    st_global_256(out_row + c * 32 + 16, o1);
-                  } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t*>(out_row + c * 32 + 2 * i) = pk[c][i];
-                  }
-                }
+                uint32_t w0, w1, w2, w3, s0, s1;
+                quant::nvfp4_block_packed<OutT, true>(lo, rq_ts, w0, w1, s0);
+                quant::nvfp4_block_packed<OutT, true>(hi, rq_ts, w2, w3, s1);
+                *reinterpret_cast<uint4*>(p.rq_codes + static_cast<int64_t>(row) * (p.N >> 1) + (col >> 1)) =
+                    make_uint4(w0, w1, w2, w3);
+                scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
               }
-              if (p.rq_codes != nullptr) {
-                if (row < p.M) {
-                  uint32_t lo[8], hi[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    lo[i] = pk[c][i];
-                    hi[i] = pk[c][8 + i];
-                  }
-                  uint32_t w0, w1, w2, w3, s0, s1;
-                  quant::nvfp4_block_packed<OutT, true>(lo, rq_ts, w0, w1, s0);
-                  quant::nvfp4_block_packed<OutT, true>(hi, rq_ts, w2, w3, s1);
-                  *reinterpret_cast<uint4*>(p.rq_codes + static_cast<int64_t>(row) * (p.N >> 1) + (col >> 1)) =
-                      make_uint4(w0, w1, w2, w3);
-                  scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
-                }
-                if ((c & 1) && row < rows_pad) {
-                  const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
-                  *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
-                  scale_word = 0;
-                }
+              if ((c & 1) && row < rows_pad) {
+                // rows between M and the next multiple of 128 are padding of the scale tensor: zero
+                // this chunk and the previous one cover scale columns (col/16 - 2) .. (col/16 + 1)
+                const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
+                *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
+                scale_word = 0;
               }
             }
           }
@@ -817,8 +843,6 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 scale_word |= (s0 | (s1 << 8)) << (16 * (c & 1));
               }
               if ((c & 1) && row < rows_pad) {
-                // rows between M and the next multiple of 128 are padding of the scale tensor: zero
-                // this chunk and the previous one cover scale columns (col/16 - 2) .. (col/16 + 1)
                 const int64_t off = swizzled_scale_offset(row, (col >> 4) - 2, rq_col_tiles);
                 *reinterpret_cast<uint32_t*>(p.rq_scales + off) = scale_word;
                 scale_word = 0;
