@@ -7,6 +7,8 @@ Every ``nn.Linear`` of the blocks is created, quantized to NVFP4 and released la
 (``comfy_kitchen.modules.NVFP4Linear``: dynamic activation scale, quantize kernel, tcgen05 GEMM
 with bias); attention is ``torch`` SDPA in bf16; no positional encoding (not on the measured
 path).  Parameter count of the linears at full size: 19 x 36 h^2 + 38 x 15 h^2 = 11.84 B.
+Element-wise glue is kept to one pass where torch offers it (addcmul for modulation and gated
+residuals).
 """
 from __future__ import annotations
 
@@ -59,7 +61,8 @@ def _qlinear(i: int, o: int, device, gen, make_linear):
 
 
 def _modulate(x, shift, scale):
-    return F.layer_norm(x, x.shape[-1:]) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+    # layer_norm(x) * (1 + scale) + shift in one pass over the tokens
+    return torch.addcmul(shift.unsqueeze(1), F.layer_norm(x, x.shape[-1:]), (1 + scale).unsqueeze(1))
 
 
 def _attention(q, k, v, heads):
@@ -101,27 +104,43 @@ class DoubleBlock(nn.Module):
         for x, st, m, _ in parts:
             a = attn[:, start:start + x.shape[1]]
             start += x.shape[1]
-            x = x + m[2].unsqueeze(1) * st.proj(a)
-            x = x + m[5].unsqueeze(1) * st.fc2(F.gelu(st.fc1(_modulate(x, m[3], m[4])), approximate="tanh"))
+            x = torch.addcmul(x, m[2].unsqueeze(1), st.proj(a))
+            x = torch.addcmul(x, m[5].unsqueeze(1), st.fc2(F.gelu(st.fc1(_modulate(x, m[3], m[4])), approximate="tanh")))
             outs.append(x)
         return outs[1], outs[0]
 
 
 class SingleBlock(nn.Module):
+    """One-stream block: attention and MLP branches read the same modulated input and are merged by
+    the second projection.  The fused weights [h -> 3h + 4h] and [h + 4h -> h] are kept as their
+    column / row blocks (same parameters and FLOPs), so that no split or concatenation copy of the
+    wide hidden tensor is needed and the activation is quantized once for both input projections."""
+
     def __init__(self, cfg: MMDiTConfig, device, gen, make_linear):
         super().__init__()
         h, r = cfg.hidden, cfg.mlp_ratio
         self.heads, self.h = cfg.heads, h
         self.mod = _qlinear(h, 3 * h, device, gen, make_linear)
-        self.linear1 = _qlinear(h, (3 + r) * h, device, gen, make_linear)
-        self.linear2 = _qlinear((1 + r) * h, h, device, gen, make_linear)
+        self.linear1_qkv = _qlinear(h, 3 * h, device, gen, make_linear)
+        self.linear1_mlp = _qlinear(h, r * h, device, gen, make_linear)
+        self.linear2_attn = _qlinear(h, h, device, gen, make_linear)
+        self.linear2_mlp = _qlinear(r * h, h, device, gen, make_linear)
 
     def forward(self, x, vec):
         shift, scale, gate = self.mod(F.silu(vec)).chunk(3, dim=-1)
-        y = self.linear1(_modulate(x, shift, scale))
-        q, k, v, mlp = torch.split(y, [self.h, self.h, self.h, y.shape[-1] - 3 * self.h], dim=-1)
+        xin = _modulate(x, shift, scale)
+        quantize = getattr(self.linear1_qkv, "quantize_input", None)
+        if quantize is not None:  # quantized layers: one activation quantization feeds both projections
+            b, s_, _ = xin.shape
+            xq = quantize(xin.reshape(b * s_, self.h))
+            q, k, v = self.linear1_qkv(xq).reshape(b, s_, 3 * self.h).chunk(3, dim=-1)
+            mlp = self.linear1_mlp(xq).reshape(b, s_, -1)
+        else:
+            q, k, v = self.linear1_qkv(xin).chunk(3, dim=-1)
+            mlp = self.linear1_mlp(xin)
         attn = _attention(q, k, v, self.heads)
-        return x + gate.unsqueeze(1) * self.linear2(torch.cat([attn, F.gelu(mlp, approximate="tanh")], dim=-1))
+        out = self.linear2_attn(attn) + self.linear2_mlp(F.gelu(mlp, approximate="tanh"))
+        return torch.addcmul(x, gate.unsqueeze(1), out)
 
 
 class MMDiTStack(nn.Module):

@@ -63,6 +63,11 @@ class _QuantizedLinearBase(nn.Module):
     def _quantize_input(self, x: torch.Tensor) -> QuantizedTensor:
         raise NotImplementedError
 
+    def quantize_input(self, x: torch.Tensor) -> QuantizedTensor:
+        """Quantize a 2-D activation the way ``forward`` would, for callers that feed the same
+        activation to several layers (pass the result to each layer's ``forward``)."""
+        return self._quantize_input(x if x.is_contiguous() else x.contiguous())
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if isinstance(x, QuantizedTensor):
             return quantized_linear(x, self.weight, self.bias)
