@@ -4,22 +4,25 @@
 //   MXFP8: A, B E4M3 bytes,                  E8M0 scale per 32 elements  (kind::mxf8f6f4)
 //
 // One persistent CTA per SM (or, for large problems, one CTA pair per two SMs computing
-// 256 x 256 tiles with cta_group::2 instructions), ten warps with fixed roles:
-//   warp 0    TMA producer: per pipeline stage one 128-row x 128-byte box of A, one
-//             TILE_N-row box of B (128-byte swizzle) and the matching 512-byte scale tiles
-//             (linear bulk copies - in the tiled scale layout the tiles a stage needs are
-//             contiguous in global memory) into a STAGES-deep shared-memory ring.
+// 256 x 256 tiles with cta_group::2 instructions), warps with fixed roles:
+//   warp 0    TMA producer: per pipeline stage one 128-row x 128-byte box of A, one box of B
+//             (128-byte swizzle) and the matching 512-byte scale tiles (linear bulk copies, or
+//             3-D tensor maps in a pair) into a STAGES-deep shared-memory ring.
 //   warp 1    MMA issuer: copies the stage's scale tiles shared -> tensor memory
 //             (tcgen05.cp), issues four tcgen05.mma per stage (32 bytes of K each) into a
 //             fp32 accumulator in tensor memory, and releases the stage / publishes the
 //             accumulator with tcgen05.commit.
-//   warps 2-9 epilogue: tcgen05.ld the accumulator into registers (two warps per 32-lane
-//             quarter, half the columns each), hand the accumulator back at once, then
-//             scale by alpha, add bias, convert and store while the next tile computes.
-// With NUM_ACC == 2 the epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2.. epilogue (8 warps; 16 for the fused epilogue, 4 for 64-wide tiles): tcgen05.ld
+//             the accumulator into registers, hand it back at once, then alpha * acc + bias,
+//             convert, stage the rows in swizzled shared memory and write them with TMA stores
+//             while the next tile computes.  The fused variant applies GELU and re-quantizes
+//             to NVFP4 instead; split-K items store raw fp32 partial tiles to a workspace;
+//             the all-gather variant stores every tile into all ranks' results.
+// With NUM_ACC == 2 the epilogue of tile i overlaps the main loop of tile i+1 entirely.
 //
 // All synchronisation is by mbarriers with bounded waits (ck_sm100.cuh): a protocol error
-// raises the device status word instead of hanging.
+// raises the device status word instead of hanging.  Kernels are launched with programmatic
+// stream serialization; everything before griddepcontrol.wait is independent of earlier kernels.
 #include "ck_sm100.cuh"
 #include "ck_quant_math.cuh"
 
