@@ -90,27 +90,47 @@ __device__ __forceinline__ void nvfp4_block(const float (&v)[16], float g, bool 
   // quotient can overflow: divisor within 2^+-60 and amax no more than 2^20 divisors.
   // Elements so small that their residual would underflow (|x| < 2^-90) have a
   // quotient below 2^-30 and encode as (signed) zero under either formula.
-  const bool window = kFastDiv && (safe >= 0x1p-60f) && (safe <= 0x1p60f) && (amax <= safe * 0x1p20f);
-  if (window) {
-    const float y = __frcp_rn(safe);
+  const bool window = kFastDiv && (safe >= 0x1p-60f) && (safe <= 0x1p60f);
+  // :154-158 clamp to +-6, round to E2M1 (satfinite does the clamp), pack two per byte.
+  auto pack = [&](const float (&e)[16]) {
+    uint32_t b[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
-  } else {
+    for (int i = 0; i < 8; ++i) {
+      b[i] = hi_first ? f32x2_to_e2m1_byte(e[2 * i], e[2 * i + 1]) : f32x2_to_e2m1_byte(e[2 * i + 1], e[2 * i]);
+    }
+    lo_word = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    hi_word = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+  };
+  bool done = false;
+  if (window) {
+    // Codes from the two products that bracket the exact quotient (see nvfp4_block_packed);
+    // accepted when they agree, which is the rule for all but a few blocks in ten thousand.
+    const float y = __frcp_rn(safe);
+    const float y_hi = __fmul_rn(y, 0x1.000008p0f), y_lo = __fmul_rn(y, 0x1.fffffp-1f);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = v[i] * y_hi;
+    pack(q);
+    const uint32_t lo_a = lo_word, hi_a = hi_word;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = v[i] * y_lo;
+    pack(q);
+    done = ((lo_a ^ lo_word) | (hi_a ^ hi_word)) == 0u;
+    if (!done && amax <= safe * 0x1p20f) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) q[i] = div_markstein(v[i], safe, y);
+      pack(q);
+      done = true;
+    }
+  }
+  if (!done) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], safe);  // :149
+    pack(q);
   }
-  if (dead) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = 0.0f;  // :150 (positive zero, sign dropped)
+  if (dead) {  // :150 (positive zeros, signs dropped)
+    lo_word = 0;
+    hi_word = 0;
   }
-  // :154-158 clamp to +-6, round to E2M1 (satfinite does the clamp), pack two per byte.
-  uint32_t b[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    b[i] = hi_first ? f32x2_to_e2m1_byte(q[2 * i], q[2 * i + 1]) : f32x2_to_e2m1_byte(q[2 * i + 1], q[2 * i]);
-  }
-  lo_word = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-  hi_word = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
 }
 
 // ---------------------------------------------------------------------------
