@@ -221,3 +221,10 @@ def test_split_k_for_small_m_long_k(ck, cuda_device, shape):
     _check_nvfp4(ck, cuda_device, a, b, None, torch.float32)
     _check_mxfp8(ck, cuda_device, a, b, bias, torch.bfloat16)
     assert gemm_status() == 0
+    # the partial tiles are added in a fixed order: two runs give the same bits
+    sa, sb = layout_scale(a), layout_scale(b)
+    qa, bsa = ck.quantize_nvfp4(a.to(cuda_device), sa.to(cuda_device), pad_16x=(m % 16 != 0))
+    qb, bsb = ck.quantize_nvfp4(b.to(cuda_device), sb.to(cuda_device))
+    runs = [ck.scaled_mm_nvfp4(qa, qb, sa.to(cuda_device), sb.to(cuda_device), bsa, bsb, bias=bias.to(cuda_device))
+            for _ in range(3)]
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
