@@ -13,12 +13,15 @@ rank runs the same step on its own data (the batch shards data-parallel, no coll
 on the data path), and the value is the aggregate over ranks.
 
 Other cases time one kernel alone (used for profiling and the per-kernel rooflines):
-quantize_nvfp4, quantize_mxfp8, gemm_nvfp4, gemm_mxfp8, linear_mxfp8.
+quantize_nvfp4, quantize_mxfp8, dequantize_nvfp4, dequantize_mxfp8, tensor_scale, gemm_nvfp4,
+gemm_mxfp8, linear_mxfp8; or another workload: mlp_pair (fc1 + GELU + re-quantize + fc2),
+sharded_gemm (N column-sharded over the ranks, fused all-gather vs NCCL), mmdit (full-model
+harness, batch split over the ranks).
 
 The JSON line also carries: ``e2e`` (the same step through the public Python API with
 host buffers: pinned-host x -> device, linear, bf16 result -> host), ``roofline`` for the
-dominant kernel (the GEMM), ``roofline_quantize``, ``cpu_baseline`` (the numpy oracle of
-the same path timed on the host), ``clocks`` sampled during the timed region, and
+dominant kernel (the GEMM), ``roofline_quantize``, ``cpu_baseline`` (the CPU oracle of the
+same path timed on the host cores, rank 0 of a one-GPU run only), ``clocks`` sampled during the timed region, and
 ``gpu_launches``.
 
 --impl reference times the CPU restatement of the reference's eager path (oracle/) on the
@@ -758,7 +761,7 @@ def run_gpu_arm(args) -> dict | None:
                        "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": per,
                        "api": "comfy_kitchen.quantize_nvfp4 + comfy_kitchen.scaled_mm_nvfp4 (pinned host x in, bf16 result out)",
                        "steps_in_flight": e2e.get("lanes", 1)}
-    if args.case == "linear" and not args.skip_extras and not args.no_cpu_baseline:
+    if args.case == "linear" and not args.skip_extras and not args.no_cpu_baseline and world == 1:
         import torch as _t
 
         _t.set_num_threads(cpu_threads())
