@@ -462,7 +462,7 @@ def run_mlp_pair(args, torch, ck, backend, device, clocks_cls, local_rank) -> di
     quantize(h), fc2 - the reference's sequence of kernels."""
     import torch.nn.functional as F
 
-    m, d, hdim = 4608, 3072, 12288
+    m, d, hdim = (args.rows or 4608), 3072, 12288
     g = torch.Generator(device="cpu").manual_seed(0)
     x = torch.randn(m, d, generator=g).bfloat16().to(device)
     w1 = (torch.randn(hdim, d, generator=g) * 0.02).bfloat16().to(device)
@@ -490,6 +490,31 @@ def run_mlp_pair(args, torch, ck, backend, device, clocks_cls, local_rank) -> di
         h = F.gelu(ck.scaled_mm_nvfp4(qx, q1, sx, s1, bsx, b1), approximate="tanh")
         hq, hqs = ck.quantize_nvfp4(h, sh)
         return ck.scaled_mm_nvfp4(hq, q2, sh, s2, hqs, b2)
+
+    if args.case == "fc1_fused":
+        # the fused kernel alone, launched from the host (profiling case)
+        qx, bsx = ck.quantize_nvfp4(x, sx)
+
+        def fc1():
+            return backend.linear_nvfp4_fused(qx, q1, sx, s1, bsx, b1, activation="gelu_tanh", requant_scale=sh,
+                                              return_dense=False)
+
+        for _ in range(args.warmup):
+            fc1()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fc1()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        fl = 2.0 * m * d * hdim
+        return {"metric": "fc1_fused_tflops", "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+                "config": {"workload": f"fc1 of the DiT MLP pair with the GELU + NVFP4 re-quantize epilogue, M={m} N={hdim} K={d}",
+                           "cuda_graph": False}, "gpu_launches": args.steps}
 
     def timed(fn):
         stream = torch.cuda.Stream()
@@ -630,7 +655,7 @@ def run_gpu_arm(args) -> dict | None:
         raise SystemExit(f"cuda backend unavailable: {info['unavailable_reason']}")
     lib = backend.load_library()
     peaks, peak_kind = load_peaks()
-    if args.case == "mlp_pair":
+    if args.case in ("mlp_pair", "fc1_fused"):
         return run_mlp_pair(args, torch, ck, backend, device, ClockSampler, local_rank) if rank == 0 else None
     if args.case == "sharded_gemm":
         line = run_sharded_gemm(args, torch, ck, dist, device, rank, world, ClockSampler, local_rank)
@@ -786,7 +811,7 @@ def main():
     ap.add_argument("--case", default="linear",
                     choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "dequantize_nvfp4",
                              "dequantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
-                             "sharded_gemm", "mlp_pair", "mmdit"])
+                             "sharded_gemm", "mlp_pair", "fc1_fused", "mmdit"])
     ap.add_argument("--mmdit-blocks", default="", help="double,single block counts of --case mmdit (default 19,38)")
     ap.add_argument("--mmdit-batch", type=int, default=8, help="total batch of --case mmdit, split over the GPUs")
     ap.add_argument("--shape", default="16384,15360,3072", help="M,N,K of --case sharded_gemm")

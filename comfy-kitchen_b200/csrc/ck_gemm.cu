@@ -278,11 +278,13 @@ __device__ __forceinline__ float round_to_out(float x) {
 // evaluated as x * sigmoid(2u) = x / (1 + 2^(-2u log2 e)) with the hardware exp2 and
 // reciprocal (relative error ~1e-6, far below the rounding of a 16-bit output type).
 __device__ __forceinline__ float gelu_tanh(float x) {
-  // x * sigmoid(2u) = x / (1 + 2^(x * (k1 + k2 x^2))), k1 = -2 log2(e) sqrt(2/pi), k2 = 0.044715 k1
+  // x * sigmoid(2u) = x / (1 + 2^(x * (k1 + k2 x^2))), k1 = -2 log2(e) sqrt(2/pi), k2 = 0.044715 k1.
+  // The flush-to-zero forms only differ where 1 + 2^(..) exceeds 2^126, i.e. where the exact
+  // result is a zero anyway (x below about -10).
   const float w = fmaf(-0.10294324f, x * x, -2.3022082f);
   float t, r;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(t) : "f"(x * w));
-  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + t));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(x * w));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + t));
   return x * r;
 }
 
