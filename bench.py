@@ -538,7 +538,6 @@ def run_mlp_pair(args, torch, ck, backend, device, clocks_cls, local_rank) -> di
     with clocks_cls(local_rank) as clocks:
         ms_fused = timed(fused)
         ms_unfused = timed(unfused)
-    same = bool(torch.equal(fused(), unfused())) if False else None
     rel = float((fused().float() - unfused().float()).norm() / unfused().float().norm())
     flops = 2.0 * 2 * m * d * hdim
     return {
