@@ -1059,8 +1059,8 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[5], co
   if (config == 0) {
     const int64_t pair_tiles = ceil_div(p.M, 256) * ceil_div(p.N, 256);
     const int64_t tiles256 = ceil_div(p.M, kTileM) * ceil_div(p.N, 256);
-    if (pair_tiles >= sm_count() / 2) {
-      config = 4;
+    if (pair_tiles * 4 >= sm_count()) {
+      config = 4;  // measured: from about a quarter of the SM count in pair tiles the pair wins
     } else if (tiles256 >= sm_count()) {
       config = 3;
     } else if (ceil_div(p.M, kTileM) * ceil_div(p.N, 128) * 4 <= sm_count()) {

@@ -133,10 +133,10 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
 // once, and a block of 32 x 8 threads walks row groups with a grid stride so that every SM
 // holds the same amount of work.
 #ifndef CK_Q_MINBLOCKS
-#define CK_Q_MINBLOCKS 4
+#define CK_Q_MINBLOCKS 2
 #endif
 #ifndef CK_Q_ROWS
-#define CK_Q_ROWS 8
+#define CK_Q_ROWS 16
 #endif
 constexpr int kPairRows = CK_Q_ROWS;  // rows per thread block; 32 lanes x 2 blocks x 16 = 1024 columns per warp
 
