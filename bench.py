@@ -552,6 +552,54 @@ def run_mlp_pair(args, torch, ck, backend, device, clocks_cls, local_rank) -> di
     }
 
 
+def run_gemm_sweep(args, torch, ck, device) -> dict:
+    """NVFP4 GEMM over the sweep of config 4 on one GPU: M in {1, 16, 256, 4096, 16384} x
+    (K, N) in {(3072, 3072), (3072, 12288), (12288, 3072), (3072, 15360)}, bf16 output, through
+    ``ck.scaled_mm_nvfp4`` (split-K workspace path included), 20 launches per CUDA-graph replay,
+    operands L2-resident where they fit."""
+    rows = []
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    for (k, n) in ((3072, 3072), (3072, 12288), (12288, 3072), (3072, 15360)):
+        w = (torch.randn(n, k, generator=gen) * 0.02).bfloat16().to(device)
+        sw = (w.abs().amax() / 2688.0).float()
+        qw, bsw = ck.quantize_nvfp4(w, sw)
+        del w
+        for m in (1, 16, 256, 4096, 16384):
+            x = torch.randn(m, k, generator=gen).bfloat16().to(device)
+            sx = (x.abs().amax() / 2688.0).float()
+            qx, bsx = ck.quantize_nvfp4(x, sx, pad_16x=(m % 16 != 0))
+
+            def f():
+                return ck.scaled_mm_nvfp4(qx, qw, sx, sw, bsx, bsw)
+
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    f()
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for _ in range(20):
+                        f()
+                graph.replay()
+                stream.synchronize()
+                best = 1e9
+                for _ in range(3):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    graph.replay()
+                    e1.record(stream)
+                    torch.cuda.synchronize()
+                    best = min(best, e0.elapsed_time(e1) / 20)
+            rows.append({"M": m, "N": n, "K": k, "us": best * 1e3, "tflops": 2.0 * m * n * k / (best * 1e-3) / 1e12})
+    big = [r for r in rows if r["M"] >= 4096]
+    return {"metric": "nvfp4_gemm_sweep_tflops", "value": sum(r["tflops"] for r in big) / len(big), "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": 20, "warmup": 3, "ms_per_step": sum(r["us"] for r in rows) * 1e-3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": "NVFP4 GEMM sweep of config 4 on one GPU (value = mean TFLOP/s of the M >= 4096 shapes)"},
+            "shapes": rows, "gpu_launches": 20 * len(rows)}
+
+
 def run_mmdit(args, torch, dist, device, rank, world, clocks_cls, local_rank) -> dict | None:
     """Random-init MMDiT-shaped stack, every block linear through NVFP4 QuantizedTensors, batch 8 split
     data-parallel over the ranks (strong scaling, no collective inside the forward)."""
@@ -654,6 +702,8 @@ def run_gpu_arm(args) -> dict | None:
         raise SystemExit(f"cuda backend unavailable: {info['unavailable_reason']}")
     lib = backend.load_library()
     peaks, peak_kind = load_peaks()
+    if args.case == "gemm_sweep":
+        return run_gemm_sweep(args, torch, ck, device) if rank == 0 else None
     if args.case in ("mlp_pair", "fc1_fused"):
         return run_mlp_pair(args, torch, ck, backend, device, ClockSampler, local_rank) if rank == 0 else None
     if args.case == "sharded_gemm":
@@ -810,7 +860,7 @@ def main():
     ap.add_argument("--case", default="linear",
                     choices=["linear", "linear_mxfp8", "tensor_scale", "quantize_nvfp4", "quantize_mxfp8", "dequantize_nvfp4",
                              "dequantize_mxfp8", "gemm_nvfp4", "gemm_mxfp8",
-                             "sharded_gemm", "mlp_pair", "fc1_fused", "mmdit"])
+                             "sharded_gemm", "gemm_sweep", "mlp_pair", "fc1_fused", "mmdit"])
     ap.add_argument("--mmdit-blocks", default="", help="double,single block counts of --case mmdit (default 19,38)")
     ap.add_argument("--mmdit-batch", type=int, default=8, help="total batch of --case mmdit, split over the GPUs")
     ap.add_argument("--shape", default="16384,15360,3072", help="M,N,K of --case sharded_gemm")
