@@ -57,7 +57,6 @@ _SIGNATURES = {
     "ck_nvfp4_tensor_scale": [_P, _I, _L, _P, _P, _L, _P],
     "ck_nvfp4_tensor_scale_noalloc": [_P, _I, _L, _P, _P],
     "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
-    "ck_debug_resident_pairs": [],
     "ck_scaled_mm_nvfp4_allgather": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8_allgather": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "ck_peer_barrier": [_P, _I, _I, ctypes.c_uint32, _P],

@@ -8,21 +8,25 @@
 //   warp 0    TMA producer: per pipeline stage one 128-row x 128-byte box of A, one box of B
 //             (128-byte swizzle) and the matching 512-byte scale tiles (linear bulk copies, or
 //             3-D tensor maps in a pair) into a STAGES-deep shared-memory ring.
-//   warp 1    MMA issuer: copies the stage's scale tiles shared -> tensor memory
-//             (tcgen05.cp), issues four tcgen05.mma per stage (32 bytes of K each) into a
-//             fp32 accumulator in tensor memory, and releases the stage / publishes the
-//             accumulator with tcgen05.commit.
+//   warp 1    MMA issuer: four tcgen05.mma per stage (32 bytes of K each) into a fp32
+//             accumulator in tensor memory; releases the stage / publishes the accumulator with
+//             tcgen05.commit.  Nothing else: the issue slot of this warp is the resource that
+//             decides whether the tensor pipe stays busy.
 //   warps 2.. epilogue (8 warps; 16 for the fused epilogue, 4 for 64-wide tiles): tcgen05.ld
 //             the accumulator into registers, hand it back at once, then alpha * acc + bias,
 //             convert, stage the rows in swizzled shared memory and write them with TMA stores
-//             while the next tile computes.  The fused variant applies GELU and re-quantizes
-//             to NVFP4 instead; split-K items store raw fp32 partial tiles to a workspace;
-//             the all-gather variant stores every tile into all ranks' results.
+//             while the next tile computes The fused variant applies GELU and
+//             re-quantizes to NVFP4 instead; split-K items store raw fp32 partial tiles to a
+//             workspace; the all-gather variant stores every tile into all ranks' results.
+//   last warp scale copier: copies each landed stage's scale tiles shared -> tensor memory
+//             (tcgen05.cp, up to 12 per stage) and tells the MMA warp through a barrier of
+//             its own.  The tensor-memory scale columns are buffered per stage like the ring.
 // With NUM_ACC == 2 the epilogue of tile i overlaps the main loop of tile i+1 entirely.
 //
 // All synchronisation is by mbarriers with bounded waits (ck_sm100.cuh): a protocol error
 // raises the device status word instead of hanging.  Kernels are launched with programmatic
-// stream serialization; everything before griddepcontrol.wait is independent of earlier kernels.
+// stream serialization; each role waits for the previous kernel (griddepcontrol.wait) only
+// before its own first global access.
 #include "ck_sm100.cuh"
 #include "ck_quant_math.cuh"
 
@@ -47,17 +51,10 @@ constexpr int kMmaKBytes = 32;      // bytes of K per tcgen05.mma
 constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
 // Epilogue warps per CTA: two per 32-lane quarter of tensor memory for the plain epilogue,
 // four for the fused one (its activation + quantization arithmetic is ~30 instructions per
-// element and must keep up with the tensor pipe).
-// A CTA pair with 192-wide tiles uses three (64 columns each, whole 128-byte store boxes), a
-// 64-wide tile one.
-#ifndef CK_FUSED_WARPS
-#define CK_FUSED_WARPS 16
-#endif
-constexpr int epilogue_warps(bool fused, int tile_n, int ctas) {
-  return (fused && tile_n >= 256) ? CK_FUSED_WARPS : (ctas == 2 && tile_n == 192) ? 12 : (tile_n <= 64) ? 4 : 8;
-}
-constexpr int num_threads(bool fused, int tile_n, int ctas) {
-  return 64 + 32 * epilogue_warps(fused, tile_n, ctas);  // + TMA, MMA warps
+// element and must keep up with the tensor pipe), one for a 64-wide tile.
+constexpr int epilogue_warps(bool fused, int tile_n) { return (fused && tile_n >= 256) ? 16 : (tile_n <= 64) ? 4 : 8; }
+constexpr int num_threads(bool fused, int tile_n) {
+  return 96 + 32 * epilogue_warps(fused, tile_n);  // + TMA, MMA and scale-copy warps
 }
 constexpr int kTmemCols = 512;
 
@@ -85,7 +82,7 @@ struct Config {
   static constexpr int kSfaBytes = kSfTilesPerStage * 512;
   static constexpr int kSfbBytes = kSfbRowBlocks * kSfTilesPerStage * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kOutStageBytes = OUT_STAGE * epilogue_warps(false, TILE_N, CTAS) * 4096;
+  static constexpr int kOutStageBytes = OUT_STAGE * epilogue_warps(false, TILE_N) * 4096;
   static constexpr int kRingBytes = (STAGES * kStageBytes + 1023) / 1024 * 1024;
   static constexpr int kSmemBytes = kRingBytes + kOutStageBytes + 3 * TILE_N * 4 /*bias*/ +
                                     1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -96,12 +93,10 @@ struct Config {
   static constexpr int kSfbCol = kSfaCol + kSfaColsPerStage;  // within one scale buffer
   static constexpr int kSfbColsPerTile = kSfbRowBlocks * 4;
   static constexpr int kSfbColsPerStage = kSfTilesPerStage * kSfbColsPerTile;
-  // The scale columns are multi-buffered like the shared-memory ring, so that the copies
-  // of the next stage do not have to wait for the MMAs still reading the previous ones.
+  // One set of scale columns per ring stage: the copy of stage s lands in set s, which the
+  // stage's "empty" barrier (MMAs retired) frees together with the shared-memory slot.
   static constexpr int kSfColsPerBuf = kSfaColsPerStage + kSfbColsPerStage;
-  static constexpr int kSfBufsFit = (kTmemCols - kSfaCol) / kSfColsPerBuf;
-  static constexpr int kSfBufs = kSfBufsFit < STAGES ? kSfBufsFit : STAGES;
-  static_assert(kSfBufs >= 1, "tensor memory budget exceeded");
+  static_assert(kSfaCol + STAGES * kSfColsPerBuf <= kTmemCols, "tensor memory budget exceeded");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
   static_assert(CTAS == 1 || TILE_N % 32 == 0, "a CTA pair needs N % 32 == 0");
   static_assert(TILE_N % 16 == 0 && TILE_N >= 16 && TILE_N <= 256, "invalid MMA N");
@@ -131,6 +126,7 @@ struct GemmParams {
   int splits;              // split-K: work items per tile (1 = off); item s of a tile covers pipeline stages
   int k_stages_per_split;  //   [s * k_stages_per_split, ...) and stores its raw fp32 partial to destination s
   int* status;             // device status word: set non-zero when a wait gave up
+  int trace_launch;        // sequence number of the launch (timeline builds only)
   // fused epilogue (FUSED kernels only)
   int activation;          // CK_ACT_*
   uint8_t* rq_codes;       // [M, N/2] NVFP4 codes of the (activated) output, or null
@@ -154,6 +150,21 @@ constexpr int kTraceTiles = 40;
 constexpr int kTraceSlots = 16;
 __device__ long long g_trace[160 * kTraceTiles * kTraceSlots];
 __device__ long long g_trace2[160 * 4 * 64];
+// per launch (ring of 8) and CTA: global timer (ns) and SM clock at entry, after the dependency wait, at exit
+__device__ long long g_trace3[8 * 160 * 8];
+__device__ __forceinline__ long long global_timer_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define CK_TRACE3(slot)                                                                              \
+  do {                                                                                               \
+    if (threadIdx.x == 0 && blockIdx.x < 160) {                                                      \
+      long long* t3 = g_trace3 + ((p.trace_launch & 7) * 160 + blockIdx.x) * 8 + 2 * (slot);         \
+      t3[0] = global_timer_ns();                                                                     \
+      t3[1] = clock64();                                                                             \
+    }                                                                                                \
+  } while (0)
 #define CK_TRACE2(kind, idx)                                                                         \
   do {                                                                                               \
     if (lane == 0 && (idx) < 64 && blockIdx.x < 160) g_trace2[(blockIdx.x * 4 + (kind)) * 64 + (idx)] = clock64(); \
@@ -169,6 +180,9 @@ __device__ long long g_trace2[160 * 4 * 64];
       g_trace[(blockIdx.x * kTraceTiles + tile_it) * kTraceSlots + (slot)] = clock64();             \
   } while (0)
 #else
+#define CK_TRACE3(slot) \
+  do {                  \
+  } while (0)
 #define CK_TRACE(slot) \
   do {                 \
   } while (0)
@@ -298,14 +312,20 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
 // caller would see), optionally stores it, and optionally re-quantizes it to NVFP4 (codes +
 // tiled block scales against a static per-tensor scale) as the A operand of the next GEMM.
 template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED, int OUT_STAGE>
-__global__ void __launch_bounds__(num_threads(FUSED, TILE_N, CTAS), 1)
+__global__ void __launch_bounds__(num_threads(FUSED, TILE_N), 1)
 block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                          const __grid_constant__ OutputMaps maps_out, const GemmParams p) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OUT_STAGE>;
   static_assert(!(FUSED && OUT_STAGE != 0), "the fused epilogue stores from registers");
-  constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N, CTAS);
-  // In a CTA pair, rank 0 (the leader) issues the MMAs for both CTAs.
+  constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N);
+  constexpr int kScaleWarp = 2 + kNumEpilogueWarps;
+  constexpr int kThreads = num_threads(FUSED, TILE_N);
+  static_assert(TILE_N <= 32 * kNumEpilogueWarps, "one bias value per epilogue thread");
+  // Everything the kernel does until a role's griddepcontrol.wait is independent of the kernel
+  // before it in the stream, so the next kernel may be scheduled as early as resources allow.
+  pdl_launch_dependents();
+  // In a CTA pair, rank 0 (the leader) issues the MMAs and scale copies for both CTAs.
   const uint32_t cta_rank = (CTAS == 2) ? cluster_cta_rank() : 0u;
   const int worker = blockIdx.x / CTAS;        // index of this CTA (pair) among the tile workers
   const int num_workers = gridDim.x / CTAS;
@@ -319,43 +339,65 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem_out = smem + Cfg::kRingBytes;  // 1024-byte aligned (swizzled store boxes)
   float* smem_bias = reinterpret_cast<float*>(smem_out + Cfg::kOutStageBytes);  // [3][TILE_N]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bias + 3 * TILE_N);
-  uint64_t* full_bar = bars;                       // [STAGES] producer -> MMA
-  uint64_t* empty_bar = bars + STAGES;             // [STAGES] MMA -> producer
-  uint64_t* acc_full_bar = bars + 2 * STAGES;      // [NUM_ACC] MMA -> epilogue
+  uint64_t* full_bar = bars;                       // [STAGES] producer -> scale copier (operands and scales landed)
+  uint64_t* empty_bar = bars + STAGES;             // [STAGES] MMA -> producer (stage and its scale columns free)
+  uint64_t* sf_full_bar = bars + 2 * STAGES;       // [STAGES] scale copier -> MMA (scales in tensor memory)
+  uint64_t* acc_full_bar = bars + 3 * STAGES;      // [NUM_ACC] MMA -> epilogue
   uint64_t* acc_empty_bar = acc_full_bar + NUM_ACC;  // [NUM_ACC] epilogue -> MMA
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + NUM_ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  static_assert((3 * STAGES + 2 * NUM_ACC) * 8 + 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  CK_TRACE3(0);
 
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+  // ------------------------------------------------------------------ set-up
+  // The producer warp creates the barriers and goes straight to its loads; the other warps
+  // meet it at a named barrier it only arrives on (tensor memory is allocated meanwhile).
+  // In a pair, every thread arrives on the cluster barrier at once and waits where it first
+  // needs the other CTA's barriers to exist.
+  uint32_t tmem_base = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      *abort_flag = 0;
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], 1);
+        mbar_init(&sf_full_bar[s], 1);
+      }
+      for (int a = 0; a < NUM_ACC; ++a) {
+        mbar_init(&acc_full_bar[a], 1);
+        mbar_init(&acc_empty_bar[a], kNumEpilogueWarps * CTAS);  // one arrival per epilogue warp (of both CTAs)
+      }
+      fence_barrier_init();
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      if constexpr (CTAS == 2) {
+        prefetch_tensormap(&map_sfa);
+        prefetch_tensormap(&map_sfb);
+      }
+      if constexpr (OUT_STAGE != 0) {
+        for (int d = 0; d < p.n_out; ++d) prefetch_tensormap(&maps_out.m[d]);
+      }
+      __threadfence_block();
     }
-    for (int a = 0; a < NUM_ACC; ++a) {
-      mbar_init(&acc_full_bar[a], 1);
-      mbar_init(&acc_empty_bar[a], kNumEpilogueWarps * CTAS);  // one arrival per epilogue warp (of both CTAs)
+    __syncwarp();
+    if constexpr (CTAS == 2) {
+      cluster_arrive();
+      cluster_wait();  // the other CTA's barriers exist before this one's loads report to them
     }
-    fence_barrier_init();
-    prefetch_tensormap(&map_a);
-    prefetch_tensormap(&map_b);
-    if constexpr (OUT_STAGE != 0) {
-      for (int d = 0; d < p.n_out; ++d) prefetch_tensormap(&maps_out.m[d]);
-    }
+    named_barrier_arrive(2, kThreads);
+  } else {
+    if constexpr (CTAS == 2) cluster_arrive();
+    if (warp == 1) tmem_alloc<CTAS>(tmem_base_slot, kTmemCols);
+    tc_fence_before_sync();
+    named_barrier_sync(2, kThreads);
+    if constexpr (CTAS == 2) cluster_wait();
+    tc_fence_after_sync();
+    tmem_base = *tmem_base_slot;
   }
-  if (warp == 1) tmem_alloc<CTAS>(tmem_base_slot, kTmemCols);
-  tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (CTAS == 2) cluster_sync_all();  // the other CTA's barriers exist before anyone signals them
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_base_slot;
-  // Everything above is independent of the kernel before this one in the stream; operands,
-  // scales and the output buffer are not.
-  pdl_launch_dependents();
-  pdl_wait();
+  CK_TRACE3(1);
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int splits = p.splits;
@@ -367,7 +409,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   // asynchronous instructions themselves are issued by one elected lane.
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    [[maybe_unused]] uint32_t it = 0;
+    pdl_wait();  // operands and scales may come from the kernel before this one
+    CK_TRACE3(2);
     int ring_s = 0;
     uint32_t ring_ph = 0;
     [[maybe_unused]] uint32_t tile_it = 0;
@@ -388,7 +431,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const bool have_sfa = (m0 / kTileM) < p.n_row_blocks_a;
       const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(m0 / kTileM) * p.sf_col_tiles * 512;
       const uint8_t* sfb_src = p.sfb + static_cast<int64_t>(rb_b0) * p.sf_col_tiles * 512;
-      for (int ks = ks_begin; ks < ks_end; ++ks, ++it) {
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         // ring position and phase as running counters (STAGES is not a power of two)
         const int s = ring_s;
         const uint32_t ph = ring_ph;
@@ -396,14 +439,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           ring_s = 0;
           ring_ph ^= 1u;
         }
-        if constexpr (CTAS == 2) {
-          mbar_wait_cluster(&empty_bar[s], ph ^ 1, abort_flag);  // signalled from the leader CTA
-        } else {
-          mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
-        }
+        mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);  // in a pair: signalled from the leader CTA
         if (ks == ks_begin) CK_TRACE(4);
         if (ks == ks_end - 1) CK_TRACE(5);
-        CK_TRACE2(0, it);
         if constexpr (CTAS == 2) {
           // Every load of both CTAs reports its bytes to the leader's barrier; scale tiles
           // come through 3-D tensor maps {512 B, column tile, row block} so that tiles past
@@ -445,8 +483,53 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         __syncwarp();
       }
     }
-  } else if (warp == 1 && cta_rank != 0) {
-    // second CTA of a pair: the leader issues the MMAs for both
+  } else if ((warp == 1 || warp == kScaleWarp) && cta_rank != 0) {
+    // second CTA of a pair: the leader issues the MMAs and the scale copies for both
+  } else if (warp == kScaleWarp) {
+    // ------------------------------------------------------------------ scale copier
+    const uint32_t sfa_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfa)));
+    const uint32_t sfb_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfb)));
+    const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
+    const uint32_t t_sfa0 = tmem_base + Cfg::kSfaCol;
+    const uint32_t t_sfb0 = tmem_base + Cfg::kSfbCol;
+    const uint32_t sf_full_addr = smem_u32(sf_full_bar);
+    int ring_s = 0;
+    uint32_t ring_ph = 0;
+    for (int item = worker; item < num_items; item += num_workers) {
+      const int tile = item / splits;
+      const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
+      const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
+        const int s = ring_s;
+        const uint32_t ph = ring_ph;
+        if (++ring_s == STAGES) {
+          ring_s = 0;
+          ring_ph ^= 1u;
+        }
+        // The previous round's MMAs on this stage have retired: the producer refilled the
+        // slot only after the stage's "empty" barrier, which their commit signalled.
+        mbar_wait(&full_bar[s], ph, abort_flag);
+        tc_fence_after_sync();
+        if (elect_one()) {
+          const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
+          const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
+          const uint32_t t_sfa = t_sfa0 + s * Cfg::kSfColsPerBuf;
+          const uint32_t t_sfb = t_sfb0 + s * Cfg::kSfColsPerBuf;
+          // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units)
+#pragma unroll
+          for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
+            tc_copy_scales_32x128b<CTAS>(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
+#pragma unroll
+            for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
+              tc_copy_scales_32x128b<CTAS>(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
+                                           desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
+            }
+          }
+          tc_commit<CTAS>(sf_full_addr + s * 8);
+        }
+        __syncwarp();
+      }
+    }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // Descriptors differ between stages only in their start-address field, so the loop
@@ -454,9 +537,6 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t a_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_a)));
     const uint32_t b_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_b)));
     const uint32_t op_hi = static_cast<uint32_t>(make_operand_desc_sw128(0) >> 32);
-    const uint32_t sfa_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfa)));
-    const uint32_t sfb_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfb)));
-    const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
     const uint32_t t_sfa0 = tmem_base + Cfg::kSfaCol;
     const uint32_t t_sfb0 = tmem_base + Cfg::kSfbCol;
     const uint32_t empty_addr = smem_u32(empty_bar);
@@ -466,7 +546,6 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     [[maybe_unused]] uint32_t it = 0;
     int ring_s = 0;
     uint32_t ring_ph = 0;
-    uint32_t sf_ring = 0;
     uint32_t tile_it = 0;
     for (int item = worker; item < num_items; item += num_workers, ++tile_it) {
       const int tile = item / splits;
@@ -485,45 +564,23 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           ring_s = 0;
           ring_ph ^= 1u;
         }
-        const uint32_t sf_buf = sf_ring * Cfg::kSfColsPerBuf;
-        if (++sf_ring == Cfg::kSfBufs) sf_ring = 0;
         CK_TRACE2(1, it);
-        if constexpr (CTAS == 2) {
-          mbar_wait_cluster(&full_bar[s], ph, abort_flag);
-        } else {
-          mbar_wait(&full_bar[s], ph, abort_flag);
-        }
+        // Scales of the stage are in tensor memory; the copier waited for the stage's loads
+        // before it issued them, so the operands have landed too.
+        mbar_wait(&sf_full_bar[s], ph, abort_flag);
         if (ks == ks_begin) CK_TRACE(2);
         if (ks == ks_end - 1) CK_TRACE(3);
         CK_TRACE2(2, it);
-#ifdef CK_GEMM_TRACE
-        if (tile_it == 1 && ks < kTraceSlots && lane == 0 && blockIdx.x < 160)
-          g_trace[(blockIdx.x * kTraceTiles + kTraceTiles - 1) * kTraceSlots + ks] = clock64();
-#endif
         tc_fence_after_sync();
         if (elect_one()) {
           const uint32_t a_lo = a_lo0 + s * (Cfg::kABytes >> 4);
           const uint32_t b_lo = b_lo0 + s * (Cfg::kBBytes >> 4);
-          const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
-          const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
           const int n_mma = min(kMmaPerStage, total_mma - ks * kMmaPerStage);
-          const uint32_t t_sfa = t_sfa0 + sf_buf;
-          const uint32_t t_sfb = t_sfb0 + sf_buf;
-          const uint32_t t_sfb_tile = t_sfb + sfb_shift;
-          // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units)
-#pragma unroll
-          for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
-            tc_copy_scales_32x128b<CTAS>(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
-#pragma unroll
-            for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
-              tc_copy_scales_32x128b<CTAS>(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
-                                           desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
-            }
-          }
+          const uint32_t t_sfa = t_sfa0 + s * Cfg::kSfColsPerBuf;
+          const uint32_t t_sfb_tile = t_sfb0 + s * Cfg::kSfColsPerBuf + sfb_shift;
           if (ks == ks_begin) {
             // Only now does the tile need its accumulator: the wait for the epilogue to have
-            // drained it comes after the first stage's operands have landed and its scale
-            // copies are issued, which takes those steps off the tile-to-tile critical path.
+            // drained it comes after the first stage has landed.
             CK_TRACE_ELECTED(0);
             mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1, abort_flag);
             CK_TRACE_ELECTED(1);
@@ -546,11 +603,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               }
             }
           }
-          // stage reusable once these MMAs and copies retire; in a pair both CTAs are told
-#ifdef CK_GEMM_TRACE
-          if (tile_it == 1 && ks < kTraceSlots && blockIdx.x < 160)
-            g_trace[(blockIdx.x * kTraceTiles + kTraceTiles - 2) * kTraceSlots + ks] = clock64();
-#endif
+          // stage (and its scale columns) reusable once these MMAs retire; in a pair both CTAs are told
           tc_commit<CTAS>(empty_addr + s * 8);
           if constexpr (CTAS == 2) tc_commit<CTAS>(empty_addr_peer + s * 8);
           if (ks == ks_end - 1) {
@@ -563,11 +616,12 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // ------------------------------------------------------------------ epilogue (warps 2 ..)
     // Two warps share each 32-lane quarter of tensor memory and split the tile's columns.
     // A warp pulls its whole share of the accumulator into registers with back-to-back
     // tcgen05.ld, hands the accumulator back to the MMA warp at once, and only then does
     // the arithmetic and the stores - so the next tile's main loop overlaps them.
+    pdl_wait();  // alpha, bias and the output buffer may belong to the kernel before this one
     const int quarter = warp & 3;  // tensor-memory lanes this warp may read: 32*quarter .. +31
     const int half = (warp - 2) >> 2;  // which share of the tile's columns
     constexpr int kColsPerWarp = TILE_N / (kNumEpilogueWarps / 4);
@@ -599,21 +653,24 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       // buffer of tile t is filled while tile t - 1 is in its epilogue (right after the drain,
       // where the warps are aligned anyway), so no barrier stands between the end of one
       // epilogue and the wait for the next accumulator.  A warp can run at most one tile ahead
-      // of the slowest one (the barrier below), hence the third buffer.
+      // of the slowest one (the barrier below), hence the third buffer.  Each epilogue thread
+      // fetches one value of the next tile before it waits for the accumulator, so the load's
+      // latency hides behind that wait.
       float* bias_s = smem_bias + (tile_it % 3) * TILE_N;
+      const bool with_bias = p.bias != nullptr && splits == 1;
       if (tile_it == 0) {
-        for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
-          const int n = n0 + c;
-          bias_s[c] = (p.bias != nullptr && n < p.N && splits == 1) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
-        }
+        if (et < TILE_N) bias_s[et] = (with_bias && n0 + et < p.N) ? load_bias(p.bias, p.bias_dtype, n0 + et) : 0.0f;
         asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
       }
-      if (warp == 2) CK_TRACE(6);
-      if constexpr (CTAS == 2) {
-        mbar_wait_cluster(&acc_full_bar[acc], acc_ph, abort_flag);
-      } else {
-        mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);
+      const int next_item = item + num_workers;
+      const bool has_next = next_item < num_items;
+      float bias_prefetched = 0.0f;
+      if (has_next && et < TILE_N) {
+        const int n = ((next_item / splits) / p.tiles_m) * TILE_N + et;
+        if (with_bias && n < p.N) bias_prefetched = load_bias(p.bias, p.bias_dtype, n);
       }
+      if (warp == 2) CK_TRACE(6);
+      mbar_wait(&acc_full_bar[acc], acc_ph, abort_flag);  // in a pair: committed from the leader CTA
       if (warp == 2) CK_TRACE(7);
       tc_fence_after_sync();
       const int c0 = half * kColsPerWarp;
@@ -652,17 +709,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           mbar_arrive(&acc_empty_bar[acc]);
         }
       }
-      {
-        const int next_item = item + num_workers;
-        if (next_item < num_items) {
-          float* bias_next = smem_bias + ((tile_it + 1) % 3) * TILE_N;
-          const int next_n0 = ((next_item / splits) / p.tiles_m) * TILE_N;
-          for (int c = et; c < TILE_N; c += 32 * kNumEpilogueWarps) {
-            const int n = next_n0 + c;
-            bias_next[c] = (p.bias != nullptr && n < p.N && splits == 1) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
-          }
-          asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
-        }
+      if (has_next) {
+        if (et < TILE_N) smem_bias[((tile_it + 1) % 3) * TILE_N + et] = bias_prefetched;
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kNumEpilogueWarps) : "memory");  // epilogue warps only
       }
       OutT* out_row = out + static_cast<int64_t>(row) * p.N + n0 + c0;
       if constexpr (!FUSED) {
@@ -677,16 +726,27 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));
             constexpr int kChunksPerBox = kBoxCols / 32;          // 2 for 16-bit outputs, 1 for fp32
             constexpr int kUnitsPerChunk = 32 * static_cast<int>(sizeof(OutT)) / 16;
+            static_assert((kChunks / kChunksPerBox - 1) * kNumEpilogueWarps * 4096 <= Cfg::kRingBytes,
+                          "the last tile's extra store boxes fit in the idle operand ring");
             const uint32_t stage_warp = smem_u32(smem_out) + (warp - 2) * (OUT_STAGE * 4096);
             const int row0 = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM + quarter * 32;
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
-              const uint32_t stage_box = stage_warp + (out_box % OUT_STAGE) * 4096;
+              // A CTA's last tile finds the operand ring idle (every load has landed and every
+              // MMA has retired before its accumulator was published): its second and later
+              // boxes are staged there, so the warp never waits for a store to release a box.
+              const bool in_ring = !has_next && c >= kChunksPerBox;
+              const uint32_t stage_box =
+                  in_ring ? smem_u32(smem) + ((c / kChunksPerBox - 1) * kNumEpilogueWarps + (warp - 2)) * 4096
+                          : stage_warp + (out_box % OUT_STAGE) * 4096;
               const uint32_t stage_row = stage_box + lane * 128;
-              if (c % kChunksPerBox == 0) {
+              if (c == 0 && warp == 2) CK_TRACE(10);
+              if (c % kChunksPerBox == 0 && !in_ring) {
                 if (lane == 0) bulk_wait_group_read<OUT_STAGE - 1>();  // the store that last used this box has read it
                 __syncwarp();
               }
+              if (c == 0 && warp == 2) CK_TRACE(11);
+              if (c == 2 && warp == 2) CK_TRACE(14);
               float v[32];
               scale_and_bias(buf[c], alpha, bias_s + c0 + c * 32, v);
 #pragma unroll
@@ -708,20 +768,15 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                   for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(v[u * 4 + j]);
                 }
                 const int unit = (c % kChunksPerBox) * kUnitsPerChunk + u;
-#ifdef CK_EXP_NOSTS
-                if (w[0] == 0x12345678u && w[3] == 0x9abcdef0u)
-#endif
                 st_shared_128(stage_row + (((unit ^ lane) & 7) << 4), w[0], w[1], w[2], w[3]);
               }
+              if (c == 0 && warp == 2) CK_TRACE(12);
+              if (c == 1 && warp == 2) CK_TRACE(13);
               if (c % kChunksPerBox == kChunksPerBox - 1) {
                 fence_proxy_async();  // the staged bytes become visible to the TMA engine
                 __syncwarp();
                 const int col = n0 + c0 + (c / kChunksPerBox) * kBoxCols;
-#ifdef CK_EXP_NOTMASTORE
-                if (lane == 0 && row0 < p.M && col < p.N && alpha == 123.456f) {
-#else
                 if (lane == 0 && row0 < p.M && col < p.N) {
-#endif
                   if (splits > 1) {
                     tma_store_2d_addr(&maps_out.m[split], stage_box, col, row0);  // this item's partial
                   } else {
@@ -731,7 +786,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 }
                 // (an empty group when nothing was stored keeps the ring's group count in step)
                 if (lane == 0) bulk_commit_group();
-                ++out_box;
+                if (c == 1 && warp == 2) CK_TRACE(15);
+                if (!in_ring) ++out_box;
               }
             }
           }
@@ -874,6 +930,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  CK_TRACE3(3);
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(p.status, 1);
     // give copies that may still be in flight time to land before the CTA's memory is released
@@ -965,11 +1022,20 @@ struct OutputSpec {
   bool plain(int64_t N) const { return n == 1 && pitch == N && col_offset == 0; }
 };
 
+// The two operand matrices (device pointers): A [M, k_bytes], B [N, k_bytes] row-major bytes.
+struct Operands {
+  const void* a;
+  const void* b;
+};
+
 template <Kind KIND, int TILE_N, int NUM_ACC, int STAGES, int CTAS, typename OutT, bool FUSED, int OUT_STAGE = 0>
-int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams p, const OutputSpec& os,
-                  cudaStream_t stream) {
+int launch_config(const Operands& ops, GemmParams p, const OutputSpec& os, cudaStream_t stream) {
   using Cfg = Config<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OUT_STAGE>;
   auto kernel = block_scaled_gemm_kernel<KIND, TILE_N, NUM_ACC, STAGES, CTAS, OutT, FUSED, OUT_STAGE>;
+  // only the tensor maps this configuration uses are encoded (host time is visible for small problems)
+  CUtensorMap map_a, map_b;
+  if (int rc = make_operand_map(&map_a, ops.a, p.M, p.k_bytes, kTileM)) return rc;
+  if (int rc = make_operand_map(&map_b, ops.b, p.N, p.k_bytes, Cfg::kBRows)) return rc;
   // the dynamic shared-memory opt-in is per device: do it once for each device that launches
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -981,7 +1047,7 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   p.tiles_m = static_cast<int>(ceil_div(p.M, Cfg::kTileRows));
   p.tiles_n = static_cast<int>(ceil_div(p.N, TILE_N));
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(num_threads(FUSED, TILE_N, CTAS));
+  cfg.blockDim = dim3(num_threads(FUSED, TILE_N));
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1010,6 +1076,8 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
   int workers = min(p.tiles_m * p.tiles_n * p.splits, resident);
 #ifdef CK_GEMM_TRACE
   if (const char* e = getenv("CK_GEMM_MAX_WORKERS")) workers = min(workers, atoi(e));
+  static std::atomic<int> launch_seq{0};
+  p.trace_launch = launch_seq.fetch_add(1);
 #endif
   cfg.gridDim = dim3(workers * CTAS);
   CUtensorMap map_sfa = {}, map_sfb = {};
@@ -1042,27 +1110,21 @@ int launch_config(const CUtensorMap& map_a, const CUtensorMap& map_b, GemmParams
 }
 
 int forced_config() {
-  // CK_GEMM_CONFIG pins the kernel configuration (tuning aid); unset = choose by shape.
-  //   1 = one CTA, 128 x 128 tiles      2 = one CTA, 128 x 192 tiles (two accumulators)
-  //   3 = one CTA, 128 x 256 tiles      4 = CTA pair, 256 x 256 tiles
-  //   5 = CTA pair, 256 x 192 tiles (two accumulators)   6 = as 4 with 4 stages and two store boxes
-  //   7 = one CTA, 128 x 64 tiles (small problems: twice the CTAs of 1)
+  // CK_GEMM_CONFIG pins the kernel configuration (used by the tests to cover each one); unset =
+  // choose by shape.
+  //   1 = one CTA, 128 x 128 tiles (two accumulators)   3 = one CTA, 128 x 256 tiles
+  //   4 = CTA pair, 256 x 256 tiles                      7 = one CTA, 128 x 64 tiles (small problems)
   const char* e = getenv("CK_GEMM_CONFIG");
   return e ? atoi(e) : 0;
 }
 
 template <Kind KIND, typename OutT, bool FUSED>
-int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[5], const GemmParams& p,
-                     const OutputSpec& os, cudaStream_t stream) {
-  // map_b[0|1|2|3|4] have boxes of 128 | 192 | 256 | 96 | 64 rows.
+int launch_for_shape(const Operands& ops, const GemmParams& p, const OutputSpec& os, cudaStream_t stream) {
   int config = forced_config();
   if (config == 0) {
     const int64_t pair_tiles = ceil_div(p.M, 256) * ceil_div(p.N, 256);
-    const int64_t tiles256 = ceil_div(p.M, kTileM) * ceil_div(p.N, 256);
     if (pair_tiles * 4 >= sm_count()) {
       config = 4;  // measured: from about a quarter of the SM count in pair tiles the pair wins
-    } else if (tiles256 >= sm_count()) {
-      config = 3;
     } else if (ceil_div(p.M, kTileM) * ceil_div(p.N, 128) * 4 <= sm_count()) {
       config = 7;  // so few 128 x 128 tiles that halving them still leaves SMs idle: more, smaller CTAs
     } else {
@@ -1070,27 +1132,18 @@ int launch_for_shape(const CUtensorMap& map_a, const CUtensorMap (&map_b)[5], co
     }
   }
   // strided / multiple destinations exist only in the configurations with a staged epilogue
-  if (!os.plain(p.N) && config != 4 && config != 6 && config != 7) config = 1;
+  if (!os.plain(p.N) && config != 4 && config != 7) config = 1;
   switch (config) {
     case 7:
-      if constexpr (!FUSED) return launch_config<KIND, 64, 2, 6, 1, OutT, false, 1>(map_a, map_b[4], p, os, stream);
-      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, os, stream);
-    case 6:
-      if constexpr (!FUSED) return launch_config<KIND, 256, 1, 4, 2, OutT, false, 2>(map_a, map_b[0], p, os, stream);
-      [[fallthrough]];
-    case 5:
-      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 5, 2, OutT, false, 1>(map_a, map_b[3], p, os, stream);
-      [[fallthrough]];
+      if constexpr (!FUSED) return launch_config<KIND, 64, 2, 6, 1, OutT, false, 1>(ops, p, os, stream);
+      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(ops, p, os, stream);
     case 4:
-      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED, FUSED ? 0 : 1>(map_a, map_b[0], p, os, stream);
+      return launch_config<KIND, 256, 1, 5, 2, OutT, FUSED, FUSED ? 0 : 1>(ops, p, os, stream);
     case 3:
-      return launch_config<KIND, 256, 1, 4, 1, OutT, FUSED>(map_a, map_b[2], p, os, stream);
-    case 2:
-      if constexpr (!FUSED) return launch_config<KIND, 192, 2, 4, 1, OutT, false>(map_a, map_b[1], p, os, stream);
-      [[fallthrough]];  // the fused epilogue needs 64-column warp shares: no 192-wide variant
+      return launch_config<KIND, 256, 1, 4, 1, OutT, FUSED>(ops, p, os, stream);
     default:
-      if constexpr (!FUSED) return launch_config<KIND, 128, 2, 5, 1, OutT, false, 1>(map_a, map_b[0], p, os, stream);
-      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(map_a, map_b[0], p, os, stream);
+      if constexpr (!FUSED) return launch_config<KIND, 128, 2, 5, 1, OutT, false, 1>(ops, p, os, stream);
+      return launch_config<KIND, 128, 2, 6, 1, OutT, FUSED>(ops, p, os, stream);
   }
 }
 
@@ -1180,6 +1233,20 @@ int launch_splitk_reduce(const float* partials, int splits, int64_t M, int64_t N
   return CK_OK;
 }
 
+// Device address of the status word on the current device (looked up once per device).
+int status_word(int** out) {
+  static std::atomic<int*> cached[64];
+  int dev = 0;
+  CK_CUDA(cudaGetDevice(&dev));
+  int* ptr = (dev >= 0 && dev < 64) ? cached[dev].load(std::memory_order_acquire) : nullptr;
+  if (ptr == nullptr) {
+    CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gemm_status));
+    if (dev >= 0 && dev < 64) cached[dev].store(ptr, std::memory_order_release);
+  }
+  *out = ptr;
+  return CK_OK;
+}
+
 struct FusedArgs {
   bool enabled = false;
   int activation = CK_ACT_NONE;
@@ -1244,15 +1311,8 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
   p.n_row_blocks_b = static_cast<int>(ceil_div(N, 128));
   p.splits = 1;
   p.k_stages_per_split = static_cast<int>(ceil_div(p.k_bytes, kStageKBytes));
-  CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
-
-  CUtensorMap map_a, map_b[5];
-  if (int rc = make_operand_map(&map_a, a, M, p.k_bytes, kTileM)) return rc;
-  if (int rc = make_operand_map(&map_b[0], b, N, p.k_bytes, 128)) return rc;
-  if (int rc = make_operand_map(&map_b[1], b, N, p.k_bytes, 192)) return rc;
-  if (int rc = make_operand_map(&map_b[2], b, N, p.k_bytes, 256)) return rc;
-  if (int rc = make_operand_map(&map_b[3], b, N, p.k_bytes, 96)) return rc;
-  if (int rc = make_operand_map(&map_b[4], b, N, p.k_bytes, 64)) return rc;
+  if (int rc = status_word(&p.status)) return rc;
+  const Operands ops = {a, b};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   OutputSpec os;
   void* const single[1] = {out};
@@ -1289,7 +1349,7 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
       ws_spec.n = plan.splits;
       ws_spec.pitch = N;
       ws_spec.col_offset = 0;
-      if (int rc = launch_config<KIND, 128, 2, 5, 1, float, false, 1>(map_a, map_b[0], ps, ws_spec, s)) return rc;
+      if (int rc = launch_config<KIND, 128, 2, 5, 1, float, false, 1>(ops, ps, ws_spec, s)) return rc;
       return launch_splitk_reduce(static_cast<const float*>(workspace), plan.splits, M, N, p, s);
     }
   }
@@ -1297,21 +1357,21 @@ int scaled_mm(const char* op, const void* a, const void* b, const void* sfa, con
     if (fused.enabled) {
       switch (out_dtype) {
         case CK_DTYPE_BF16:
-          return launch_for_shape<KIND, __nv_bfloat16, true>(map_a, map_b, p, os, s);
+          return launch_for_shape<KIND, __nv_bfloat16, true>(ops, p, os, s);
         case CK_DTYPE_F16:
-          return launch_for_shape<KIND, __half, true>(map_a, map_b, p, os, s);
+          return launch_for_shape<KIND, __half, true>(ops, p, os, s);
         default:
-          return launch_for_shape<KIND, float, true>(map_a, map_b, p, os, s);
+          return launch_for_shape<KIND, float, true>(ops, p, os, s);
       }
     }
   }
   switch (out_dtype) {
     case CK_DTYPE_BF16:
-      return launch_for_shape<KIND, __nv_bfloat16, false>(map_a, map_b, p, os, s);
+      return launch_for_shape<KIND, __nv_bfloat16, false>(ops, p, os, s);
     case CK_DTYPE_F16:
-      return launch_for_shape<KIND, __half, false>(map_a, map_b, p, os, s);
+      return launch_for_shape<KIND, __half, false>(ops, p, os, s);
     default:
-      return launch_for_shape<KIND, float, false>(map_a, map_b, p, os, s);
+      return launch_for_shape<KIND, float, false>(ops, p, os, s);
   }
 }
 
@@ -1402,33 +1462,16 @@ extern "C" int ck_scaled_mm_mxfp8_allgather(const void* a, const void* b, const 
                                          bias_dtype, out_ptrs[0], out_dtype, M, N_local, K, stream, ck::FusedArgs(), &os);
 }
 
-// Number of CTA pairs the 256x256 configuration runs concurrently on the current device
-// (diagnostic; 0 until that configuration has launched once).
-extern "C" int ck_debug_resident_pairs(void) {
-  cudaLaunchConfig_t cfg = {};
-  using Cfg = ck::Config<ck::Kind::kNvfp4, 256, 1, 5, 2, 1>;
-  auto kernel = ck::block_scaled_gemm_kernel<ck::Kind::kNvfp4, 256, 1, 5, 2, __nv_bfloat16, false, 1>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -1;
-  cfg.gridDim = dim3(ck::sm_count() / 2 * 2);
-  cfg.blockDim = dim3(ck::num_threads(false, 256, 2));
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) return -1;
-  return clusters;
-}
-
 #ifdef CK_GEMM_TRACE
 // Copies the per-tile timeline to the host: [160 CTAs][40 tiles][16 slots] of SM cycle counts.
 extern "C" __attribute__((visibility("default"))) int ck_debug_trace(long long* host_out) {
   CK_CUDA(cudaDeviceSynchronize());
   CK_CUDA(cudaMemcpyFromSymbol(host_out, ck::g_trace, sizeof(long long) * 160 * ck::kTraceTiles * ck::kTraceSlots));
+  return CK_OK;
+}
+extern "C" __attribute__((visibility("default"))) int ck_debug_trace3(long long* host_out) {
+  CK_CUDA(cudaDeviceSynchronize());
+  CK_CUDA(cudaMemcpyFromSymbol(host_out, ck::g_trace3, sizeof(long long) * 8 * 160 * 8));
   return CK_OK;
 }
 extern "C" __attribute__((visibility("default"))) int ck_debug_trace2(long long* host_out) {

@@ -80,9 +80,21 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   return r;
 }
 
+// Cluster-wide barrier in its two halves: every thread of every CTA of the cluster arrives
+// once and waits once per phase (whole warps, converged).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  cluster_arrive();
+  cluster_wait();
+}
+
+// CTA-local named barrier `id` (1..15) over `threads` threads: arrive without waiting / wait.
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // Arrive on an mbarrier of another CTA of the cluster (address from map_to_cta).  The
@@ -92,12 +104,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 // cluster-scope forms cost several hundred cycles per call.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-
-// Wait on a barrier of this CTA that the other CTA of the pair (or a tcgen05.commit issued
-// there) arrives on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  return mbar_wait(bar, parity, abort_flag);
 }
 
 // One lane of a converged warp (the same lane every time for a full warp).

@@ -275,11 +275,6 @@ CK_API int ck_peer_barrier(void* const* flag_ptrs, int rank, int world, uint32_t
  * 0 = every barrier completed, 1 + r = rank r did not arrive in time.  Host pointer. */
 CK_API int ck_peer_status(int* status_out);
 
-/* Diagnostic with no counterpart in the reference: how many 2-CTA clusters of the
- * 256x256 GEMM configuration can be resident at once on the current device
- * (negative on error). */
-CK_API int ck_debug_resident_pairs(void);
-
 /*
  * Device status word of the GEMM kernels.  Every wait inside them is bounded; a
  * wait that gives up sets the word instead of hanging.  This call synchronises
