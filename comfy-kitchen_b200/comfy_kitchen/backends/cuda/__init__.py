@@ -25,7 +25,9 @@ __all__ = [
     "scaled_mm_nvfp4",
     "scaled_mm_mxfp8",
     "linear_nvfp4_fused",
+    "linear_nvfp4_from_float",
     "nvfp4_tensor_scale",
+    "check_device_status",
 ]
 
 _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
@@ -50,6 +52,7 @@ _SIGNATURES = {
     "ck_scaled_mm_nvfp4": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P],
     "ck_gemm_status": [_P],
+    "ck_debug_set_gemm_status": [_I],
     "ck_scaled_mm_workspace_bytes": [_I, _L, _L, _L],
     "ck_scaled_mm_nvfp4_ws": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
     "ck_scaled_mm_mxfp8_ws": [_P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
@@ -57,15 +60,18 @@ _SIGNATURES = {
     "ck_nvfp4_tensor_scale": [_P, _I, _L, _P, _P, _L, _P],
     "ck_nvfp4_tensor_scale_noalloc": [_P, _I, _L, _P, _P],
     "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
+    "ck_linear_nvfp4_from_float_workspace_bytes": [_L, _L, _I],
+    "ck_linear_nvfp4_from_float": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
     "ck_scaled_mm_nvfp4_allgather": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8_allgather": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "ck_peer_barrier": [_P, _I, _I, ctypes.c_uint32, _P],
+    "ck_peer_barrier_bounded": [_P, _I, _I, ctypes.c_uint32, ctypes.c_uint32, _P],
     "ck_peer_status": [_P],
     "ck_dequantize_nvfp4": [_P, _P, _P, _P, _I, _L, _L, _I, _P],
     "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
 }
 _RESTYPE = {"ck_last_error": ctypes.c_char_p, "ck_nvfp4_tensor_scale_scratch_bytes": ctypes.c_int64,
-            "ck_scaled_mm_workspace_bytes": ctypes.c_int64}
+            "ck_scaled_mm_workspace_bytes": ctypes.c_int64, "ck_linear_nvfp4_from_float_workspace_bytes": ctypes.c_int64}
 
 
 def library_path() -> str:
@@ -197,7 +203,10 @@ def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
     key = (x.device, stream)
     scratch = _scale_scratch.get(key)
     if scratch is None or scratch.numel() < need:
-        scratch = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=x.device)
+        if scratch is not None:
+            _retired_workspaces.append(scratch)  # a captured CUDA graph may still point at it
+        # 1 MiB covers 2^33 elements: growth (an allocation and a memset) is a first-call event
+        scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
         _scale_scratch[key] = scratch
     out = torch.empty((), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
@@ -368,12 +377,17 @@ def scaled_mm_mxfp8_allgather(a, b, block_scale_a, block_scale_b, out_ptrs, n_to
     del bias_keep
 
 
-def peer_barrier(flag_ptrs, rank: int, epoch: int, device) -> None:
-    """Launch the cross-GPU barrier kernel on the current stream of ``device`` (see ck_peer_barrier)."""
+def peer_barrier(flag_ptrs, rank: int, epoch: int, device, max_polls: int | None = None) -> None:
+    """Launch the cross-GPU barrier kernel on the current stream of ``device`` (see ck_peer_barrier).
+    ``max_polls`` (about 0.5 us each, at most 2**26) replaces the default bound of about a second."""
     lib = load_library()
     arr = _pointer_array(flag_ptrs)
     with torch.cuda.device(device):
-        _check(lib.ck_peer_barrier(arr, rank, len(flag_ptrs), epoch & 0xFFFFFFFF, _stream(device)), "peer_barrier")
+        if max_polls is None:
+            _check(lib.ck_peer_barrier(arr, rank, len(flag_ptrs), epoch & 0xFFFFFFFF, _stream(device)), "peer_barrier")
+        else:
+            _check(lib.ck_peer_barrier_bounded(arr, rank, len(flag_ptrs), epoch & 0xFFFFFFFF, int(max_polls),
+                                               _stream(device)), "peer_barrier")
 
 
 def peer_status() -> int:
@@ -382,6 +396,65 @@ def peer_status() -> int:
     v = ctypes.c_int(0)
     _check(lib.ck_peer_status(ctypes.byref(v)), "peer_status")
     return v.value
+
+
+def check_device_status(what: str = "kernel") -> None:
+    """Raise RuntimeError if a bounded wait inside a GEMM kernel or the cross-GPU barrier gave up
+    since the last check.  A launch returns 0 long before its kernel runs, so this is the only
+    way to learn of such a failure; it synchronises the device, hence it is not called on the hot
+    path (the layouts call it after each call chain when ``CK_STRICT=1``, never during graph
+    capture)."""
+    lib = load_library()
+    g, b = ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib.ck_gemm_status(ctypes.byref(g)), "gemm_status")
+    _check(lib.ck_peer_status(ctypes.byref(b)), "peer_status")
+    if g.value != 0:
+        raise RuntimeError(f"{what}: a wait inside a GEMM kernel gave up (device status {g.value}); the result is invalid")
+    if b.value != 0:
+        raise RuntimeError(f"{what}: rank {b.value - 1} did not arrive at the cross-GPU barrier in time; the result is invalid")
+
+
+_linear_workspaces: dict = {}
+
+
+def linear_nvfp4_from_float(x: torch.Tensor, w_codes: torch.Tensor, w_scale: torch.Tensor, w_block_scales: torch.Tensor,
+                            bias: torch.Tensor | None = None, x_scale: torch.Tensor | None = None,
+                            out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """NVFP4 linear on a dense activation in one library call: (dynamic scale ->) quantize -> GEMM.
+
+    ``x`` [M, K] float; ``w_codes`` uint8 [N, K/2] with its tiled E4M3 ``w_block_scales`` and fp32
+    ``w_scale``; ``x_scale`` a static per-tensor scale or None for ``amax(|x|)/2688``.  Same bits
+    as ``quantize_nvfp4`` followed by ``scaled_mm_nvfp4``.  The quantized activation goes to a
+    workspace cached per device and stream (grow-only; outgrown buffers are kept alive because a
+    captured CUDA graph may still point at them)."""
+    lib = load_library()
+    x, w_codes, w_block_scales = _plain(x), _plain(w_codes), _plain(w_block_scales)
+    assert x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2-D tensor"
+    m, k = x.shape
+    n, kb = w_codes.shape
+    assert 2 * kb == k, "Matrix dimensions do not match"
+    assert k % 32 == 0 and n % 8 == 0, "K must be a multiple of 32 and N of 8"
+    assert tuple(w_block_scales.shape) == (roundup(n, 128), roundup(k // 16, 4)), "Invalid B scale shape"
+    dev = x.device
+    out_dtype = out_dtype or (x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16)
+    sw = _scalar_f32(w_scale, dev, "w_scale")
+    sx = None if x_scale is None else _scalar_f32(x_scale, dev, "x_scale")
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    need = int(lib.ck_linear_nvfp4_from_float_workspace_bytes(m, k, int(sx is None)))
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _linear_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        _linear_workspaces[key] = ws
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib.ck_linear_nvfp4_from_float(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(sx), _ptr(w_codes), _ptr(w_block_scales),
+                                              _ptr(sw), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
+                                              ws.data_ptr(), ws.numel(), _stream(dev)), "linear_nvfp4_from_float")
+    del bias_keep
+    return out
 
 
 ACTIVATIONS = {None: 0, "none": 0, "gelu_tanh": 1}

@@ -135,9 +135,16 @@ class PeerOutput:
     result may be read after :meth:`barrier` has run behind the GEMM on the same stream; with two
     or more buffers a rank can still be reading result i while its peers already write result
     i + 1.  Multicast mappings are not needed (all stores are plain peer stores).
+
+    The barrier's wait is bounded (about a second; ``first_barrier_seconds`` for the first one,
+    when ranks can be far apart because of module loading and first-call set-up).  A barrier that
+    gave up leaves a partly written result and an error status on the device, nothing else:
+    **a result is valid only if** :meth:`check` **passes** - call it wherever the host reads
+    results or at the end of a step (it synchronises the device).
     """
 
-    def __init__(self, m: int, n_total: int, dtype: torch.dtype, device, group=None, buffers: int = 2):
+    def __init__(self, m: int, n_total: int, dtype: torch.dtype, device, group=None, buffers: int = 2,
+                 first_barrier_seconds: float = 20.0):
         import torch.distributed._symmetric_memory as symm
 
         self.group = group if group is not None else dist.group.WORLD
@@ -158,6 +165,7 @@ class PeerOutput:
         self.flag_ptrs = [int(p) for p in fh.buffer_ptrs]
         self.epoch = 0
         self.turn = 0
+        self._first_polls = max(1, min(1 << 26, int(first_barrier_seconds * 2e6)))  # ~0.5 us per poll
         torch.cuda.synchronize(device)
         dist.barrier(self.group)  # every rank's flags are zero before anyone signals
 
@@ -171,7 +179,15 @@ class PeerOutput:
         from .backends import cuda as backend
 
         self.epoch += 1
-        backend.peer_barrier(self.flag_ptrs, self.rank, self.epoch, self.device)
+        backend.peer_barrier(self.flag_ptrs, self.rank, self.epoch, self.device,
+                             max_polls=self._first_polls if self.epoch == 1 else None)
+
+    def check(self) -> None:
+        """Synchronise the device and raise RuntimeError if any barrier (or GEMM wait) since the
+        last check gave up - the results produced in between are then incomplete."""
+        from .backends import cuda as backend
+
+        backend.check_device_status("sharded linear with fused all-gather")
 
 
 def sharded_linear_nvfp4_fused(qx: torch.Tensor, x_scale: torch.Tensor, x_block_scale: torch.Tensor,

@@ -24,13 +24,32 @@ def strict_mode() -> bool:
     return os.environ.get("CK_STRICT", "0") == "1"
 
 
+def strict_status_check(what: str) -> None:
+    """Under CK_STRICT=1: read the device status words after a call chain and raise if a bounded
+    wait inside a kernel gave up (a launch returns 0 long before that can be known).  Synchronises
+    the device, so it is skipped while a CUDA graph is being captured."""
+    if not strict_mode() or not torch.cuda.is_available() or torch.cuda.is_current_stream_capturing():
+        return
+    from comfy_kitchen.backends import cuda as backend
+
+    if backend.is_loaded():
+        backend.check_device_status(what)
+
+
 def direct_backend(*tensors):
     """The CUDA backend module when the kernels can be called without the operator dispatcher: all
     tensors on a CUDA device and nothing is being traced.  ``ck.<op>`` goes through a custom op and
     the backend registry (what ``torch.compile`` needs, and what CPU tensors need to raise the
     documented error); eager CUDA calls from the layouts skip those ~50 us of host work per call."""
-    if torch.compiler.is_compiling() or not all(t.is_cuda for t in tensors if isinstance(t, torch.Tensor)):
+    if torch.compiler.is_compiling():
         return None
+    for t in tensors:
+        if not isinstance(t, torch.Tensor):
+            continue
+        # fake / functional / proxy tensors (what the compiler's tracing passes hand to
+        # __torch_dispatch__) have no data pointer: only plain tensors may skip the dispatcher
+        if (type(t) is not torch.Tensor and type(t) is not torch.nn.Parameter) or not t.is_cuda:
+            return None
     from comfy_kitchen.backends import cuda as backend
 
     return backend if backend.is_loaded() else None
@@ -64,6 +83,7 @@ def quantized_linear(x: QuantizedTensor, w: QuantizedTensor, bias: torch.Tensor 
     out_dtype = out_dtype or x._params.orig_dtype
     try:
         y = layout.scaled_mm(x, w, bias, out_dtype)
+        strict_status_check(f"{layout.__name__} linear")
     except (RuntimeError, TypeError) as e:
         if strict_mode():
             raise
@@ -80,7 +100,9 @@ def install_handlers(layout, *, name: str, with_addmm: bool) -> None:
 
     def fast(dense_op, dense_args, a, b, bias, out_dtype, rows, cols, what):
         try:
-            return crop(layout.scaled_mm(a, b, bias, out_dtype), rows, cols)
+            y = crop(layout.scaled_mm(a, b, bias, out_dtype), rows, cols)
+            strict_status_check(f"{name} {what}")
+            return y
         except (RuntimeError, TypeError) as e:
             if strict_mode():
                 raise

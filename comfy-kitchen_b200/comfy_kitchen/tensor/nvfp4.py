@@ -47,10 +47,9 @@ class TensorCoreNVFP4Layout(QuantizedLayout):
             raise ValueError(f"NVFP4 requires 2D tensor, got {tensor.dim()}D")
         orig_shape = tuple(tensor.shape)
         if scale is None or (isinstance(scale, str) and scale == "recalculate"):
-            if tensor.is_cuda and tensor.is_contiguous() and tensor.dtype in (torch.bfloat16, torch.float16, torch.float32):
-                from comfy_kitchen.backends import cuda as _cuda
-
-                scale = _cuda.nvfp4_tensor_scale(tensor)  # one kernel for abs, amax and the division
+            fused = direct_backend(tensor) if tensor.is_contiguous() else None
+            if fused is not None and tensor.dtype in (torch.bfloat16, torch.float16, torch.float32):
+                scale = fused.nvfp4_tensor_scale(tensor)  # one kernel for abs, amax and the division
             else:
                 scale = torch.amax(tensor.abs()) / (F8_E4M3_MAX * F4_E2M1_MAX)
         if not isinstance(scale, torch.Tensor):
@@ -102,4 +101,8 @@ class TensorCoreNVFP4Layout(QuantizedLayout):
                                   bias=bias, out_dtype=out_dtype)
 
 
-install_handlers(TensorCoreNVFP4Layout, name="NVFP4", with_addmm=False)
+# addmm: the reference has no NVFP4 handler (its aten.addmm falls to the dequantize path); outside
+# inference mode F.linear with a bias reaches a tensor subclass as t + addmm, so without one a
+# biased linear in grad mode would leave the tensor-core path.  The handler takes the fast path
+# under the same condition as mm (b carries a deferred transpose) and falls back otherwise.
+install_handlers(TensorCoreNVFP4Layout, name="NVFP4", with_addmm=True)

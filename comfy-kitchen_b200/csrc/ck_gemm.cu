@@ -1481,6 +1481,14 @@ extern "C" __attribute__((visibility("default"))) int ck_debug_trace2(long long*
 }
 #endif
 
+// Validation aid: sets the status word from the host, so that the error path of callers can be
+// tested without making a kernel fail.
+extern "C" int ck_debug_set_gemm_status(int value) {
+  CK_CUDA(cudaDeviceSynchronize());
+  CK_CUDA(cudaMemcpyToSymbol(ck::g_gemm_status, &value, sizeof(int)));
+  return CK_OK;
+}
+
 // Device status word of the GEMM kernels: 0 = every wait completed; non-zero = some wait
 // gave up (results of that launch are invalid).  Synchronises the device; resets the word.
 extern "C" int ck_gemm_status(int* status_out) {

@@ -16,7 +16,8 @@ namespace ck {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr uint32_t kPollLimit = 1u << 20;  // x (500 ns sleep + one remote read) ~ 1 s
+constexpr uint32_t kPollLimit = 1u << 20;     // x (500 ns sleep + one remote read) ~ 1 s
+constexpr uint32_t kMaxPollLimit = 1u << 26;  // callers may raise the bound, but it stays finite (~1 min)
 
 struct PeerFlags {
   uint32_t* ptr[kMaxRanks];
@@ -33,13 +34,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-__global__ void peer_barrier_kernel(const PeerFlags flags, int rank, int world, uint32_t epoch, int* status) {
+__global__ void peer_barrier_kernel(const PeerFlags flags, int rank, int world, uint32_t epoch, uint32_t poll_limit,
+                                    int* status) {
   const int t = threadIdx.x;
   if (t >= world) return;
   __threadfence_system();
   st_release_sys(flags.ptr[t] + rank, epoch);
   const uint32_t* mine = flags.ptr[rank] + t;
-  for (uint32_t i = 0; i < kPollLimit; ++i) {
+  for (uint32_t i = 0; i < poll_limit; ++i) {
     // epochs only grow; a signed difference keeps the test valid across wrap-around
     if (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) >= 0) return;
     __nanosleep(500);
@@ -50,8 +52,11 @@ __global__ void peer_barrier_kernel(const PeerFlags flags, int rank, int world, 
 }  // namespace
 }  // namespace ck
 
-extern "C" int ck_peer_barrier(void* const* flag_ptrs, int rank, int world, uint32_t epoch, void* stream) {
+extern "C" int ck_peer_barrier_bounded(void* const* flag_ptrs, int rank, int world, uint32_t epoch, uint32_t max_polls,
+                                       void* stream) {
   using namespace ck;
+  CK_REQUIRE(max_polls >= 1 && max_polls <= kMaxPollLimit, "peer_barrier: poll limit %u outside [1, %u]", max_polls,
+             kMaxPollLimit);
   CK_REQUIRE(flag_ptrs != nullptr, "peer_barrier: null flag pointers");
   CK_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "peer_barrier: rank %d of %d", rank, world);
   PeerFlags f = {};
@@ -62,9 +67,13 @@ extern "C" int ck_peer_barrier(void* const* flag_ptrs, int rank, int world, uint
   }
   int* status = nullptr;
   CK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_peer_status));
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, rank, world, epoch, status);
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, rank, world, epoch, max_polls, status);
   CK_CUDA(cudaGetLastError());
   return CK_OK;
+}
+
+extern "C" int ck_peer_barrier(void* const* flag_ptrs, int rank, int world, uint32_t epoch, void* stream) {
+  return ck_peer_barrier_bounded(flag_ptrs, rank, world, epoch, ck::kPollLimit, stream);
 }
 
 extern "C" int ck_peer_status(int* status_out) {

@@ -196,6 +196,31 @@ CK_API int ck_linear_nvfp4_fused(const void* a, const void* b, const void* sfa, 
                           int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * NVFP4 linear on a dense activation in one call: x [M,K] (f32/f16/bf16, row-major, contiguous) is
+ * quantized to NVFP4 (codes + tiled block scales, as ck_quantize_nvfp4 with hi_first = 1 writes
+ * them) and multiplied with a pre-quantized weight:
+ *   out[M,N] = cast( deq(quantize(x)) . deq(w)^T * (x_scale * w_scale) + bias )
+ * x_scale: the activation's per-tensor scale in device memory, or NULL for the dynamic scale
+ * amax(|x|)/2688 of ck_nvfp4_tensor_scale (one more kernel).  The kernels are enqueued back to
+ * back on `stream` and chained with programmatic dependent launch; results are bit-identical to
+ * calling ck_nvfp4_tensor_scale, ck_quantize_nvfp4 and ck_scaled_mm_nvfp4 one after the other.
+ * The quantized activation is written to `workspace` (device memory, 256-byte aligned, at least
+ * ck_linear_nvfp4_from_float_workspace_bytes(M, K, x_scale == NULL) bytes; codes at offset 0).
+ * With a dynamic scale the workspace must have been zero-filled once before its first use (the
+ * scale kernel's scratch lives in it and is left zeroed by every call); calls that can overlap
+ * on the GPU need separate workspaces.  K % 32 == 0, N % 8 == 0.
+ * Replaces the sequence QuantizedTensor.from_float -> F.linear of the reference
+ * (comfy_kitchen/tensor/nvfp4.py:51-82 followed by tensor/nvfp4.py:214-264; the caller side is
+ * samples/nvfp4_linear.py:77-80).
+ */
+CK_API int64_t ck_linear_nvfp4_from_float_workspace_bytes(int64_t M, int64_t K, int dynamic_scale);
+CK_API int ck_linear_nvfp4_from_float(const void* x, int x_dtype, const float* x_scale,
+                               const void* w_codes, const void* w_block_scales, const float* w_scale,
+                               const void* bias, int bias_dtype, void* out, int out_dtype,
+                               int64_t M, int64_t N, int64_t K,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * MXFP8 GEMM with linear semantics: out[M,N] = cast(deq(a) . deq(b)^T + bias).
  * a: E4M3 bytes [M,K], b: E4M3 bytes [N,K], sfa/sfb: E8M0 block scales in the
  * swizzled layout with roundup(M|N,128) x roundup(K/32,4) bytes.  K must be a
@@ -271,19 +296,35 @@ CK_API int ck_scaled_mm_mxfp8_allgather(const void* a, const void* b, const void
  */
 CK_API int ck_peer_barrier(void* const* flag_ptrs, int rank, int world, uint32_t epoch, void* stream);
 
+/* The same barrier with the caller's bound on the wait: max_polls polls of about 0.5 us each
+ * (ck_peer_barrier uses 2^20, about a second; at most 2^26).  For the first barrier after
+ * start-up, where ranks can be seconds apart (module loading, first-call set-up), a larger
+ * bound keeps a slow rank from being reported as missing.  The results of a GEMM with a fused
+ * all-gather are valid only if ck_peer_status reports 0 afterwards. */
+CK_API int ck_peer_barrier_bounded(void* const* flag_ptrs, int rank, int world, uint32_t epoch,
+                            uint32_t max_polls, void* stream);
+
 /* Synchronises the current device and reports (then clears) the barrier status word:
  * 0 = every barrier completed, 1 + r = rank r did not arrive in time.  Host pointer. */
 CK_API int ck_peer_status(int* status_out);
 
 /*
  * Device status word of the GEMM kernels.  Every wait inside them is bounded; a
- * wait that gives up sets the word instead of hanging.  This call synchronises
+ * wait that gives up sets the word instead of hanging.  The launching call has
+ * returned CK_OK long before: a return code of 0 says the launch was accepted, not
+ * that every wait completed, so callers that need that guarantee read this word
+ * (the Python package does after each call chain when CK_STRICT=1).  This call synchronises
  * the current device, writes the word to *status_out (0 = all launches since the
  * last call completed their waits) and clears it.  Host pointer.  Not for use
  * during graph capture.  No counterpart in the reference (its GEMM is a cuBLASLt
  * call, comfy_kitchen/backends/cuda/ops/cublas_gemm_nvfp4.cu:256-272).
  */
 CK_API int ck_gemm_status(int* status_out);
+
+/* Validation aid with no counterpart in the reference: writes `value` into the GEMM status
+ * word of the current device from the host (synchronises first), so that a caller's handling
+ * of a non-zero status can be tested without making any kernel fail. */
+CK_API int ck_debug_set_gemm_status(int value);
 
 #ifdef __cplusplus
 }

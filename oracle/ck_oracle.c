@@ -216,6 +216,16 @@ void ck_oracle_f32_to_bf16(const float* x, int64_t n, uint16_t* out) {
   }
 }
 
+/* Number of OpenMP threads the row loops use from now on (a launcher may have exported
+ * OMP_NUM_THREADS=1; callers that time this code set the count they report). */
+void ck_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int ck_oracle_threads(void) {
   int n = 1;
 #ifdef _OPENMP

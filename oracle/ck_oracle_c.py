@@ -31,6 +31,8 @@ def _load():
                      "ck_oracle_dequantize_mxfp8", "ck_oracle_f32_to_bf16"):
             getattr(lib, name).restype = None
         lib.ck_oracle_threads.restype = I
+        lib.ck_oracle_set_threads.argtypes = [I]
+        lib.ck_oracle_set_threads.restype = None
         _lib = lib
     except Exception as e:  # noqa: BLE001 - no compiler, no library: callers fall back to numpy
         _error = f"{type(e).__name__}: {e}"
@@ -43,6 +45,11 @@ def available() -> bool:
 
 def threads() -> int:
     return int(_load().ck_oracle_threads())
+
+
+def set_threads(n: int) -> None:
+    """Use ``n`` OpenMP threads in the row loops from now on, whatever OMP_NUM_THREADS said at start-up."""
+    _load().ck_oracle_set_threads(int(n))
 
 
 def _roundup(x: int, m: int) -> int:

@@ -113,10 +113,17 @@ def test_mm_with_deferred_transpose_and_addmm(qt_mod, cuda_device, layout, monke
     y_mm = torch.mm(qx, qw.t())
     assert torch.equal(y_lin, y_mm)  # same kernel, same operands
     y_addmm = torch.addmm(b, qx, qw.t())
-    if layout == "TensorCoreMXFP8Layout":
-        assert torch.equal(y_addmm, F.linear(qx, qw, b))           # fused path (reference mxfp8.py:179-208)
-    else:
-        assert torch.equal(y_addmm, torch.addmm(b, qx.dequantize(), qw.dequantize().t()))  # NVFP4 has no addmm handler
+    with torch.inference_mode():
+        y_lin_bias = F.linear(qx, qw, b)
+    assert torch.equal(y_addmm, y_lin_bias)  # fused path for both layouts (reference mxfp8.py:179-208)
+    # F.linear with a bias in grad mode is decomposed into t + addmm before the subclass sees it:
+    # it must stay on the tensor-core path (CK_STRICT would raise on a failed fast path; the
+    # dequantize fallback would give different bits)
+    assert torch.equal(F.linear(qx, qw, b), y_lin_bias)
+    # b without a deferred transpose is not the kernel's layout: dense fallback, exact
+    # (reference tests/test_tensor.py:1010-1025)
+    qwt = qt_mod.QuantizedTensor.from_float(w.t().contiguous(), layout)
+    assert torch.equal(torch.addmm(b, qx, qwt), torch.addmm(b, qx.dequantize(), qwt.dequantize()))
     # dequantize of a transposed tensor
     assert torch.equal(qw.t().dequantize(), qw.dequantize().t())
 
@@ -178,3 +185,91 @@ def test_static_scale_model_under_cuda_graph(qt_mod, cuda_device, monkeypatch):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(static_y, model(x * 0.5))
+
+
+# ------------------------------------------------------------------------------------------ torch.compile
+class _TwoLayerModel(torch.nn.Module):
+    """quantize(x, static scale) -> linear -> GELU -> quantize(h, static scale) -> linear: the model of
+    the reference's integration tests (tests/test_integration.py:14-53)."""
+
+    def __init__(self, qt_mod, layout, device):
+        super().__init__()
+        g = torch.Generator(device="cpu").manual_seed(21)
+        self.layout = layout
+        self.qt = qt_mod
+        self.w1 = qt_mod.QuantizedTensor.from_float((torch.randn(128, 64, generator=g) * 0.05).bfloat16().to(device), layout)
+        self.w2 = qt_mod.QuantizedTensor.from_float((torch.randn(32, 128, generator=g) * 0.05).bfloat16().to(device), layout)
+        self.b1 = (torch.randn(128, generator=g) * 0.01).bfloat16().to(device)
+        self.input_scale = torch.tensor(48.0 / 2688.0, device=device)
+        self.hidden_scale = torch.tensor(96.0 / 2688.0, device=device)
+
+    def _q(self, t, scale):
+        if self.layout == "TensorCoreNVFP4Layout":
+            return self.qt.QuantizedTensor.from_float(t, self.layout, scale=scale)
+        return self.qt.QuantizedTensor.from_float(t, self.layout)
+
+    def forward(self, x):
+        h = F.gelu(F.linear(self._q(x, self.input_scale), self.w1, self.b1))
+        return F.linear(self._q(h, self.hidden_scale), self.w2)
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("compile_backend", ["aot_eager", "inductor"])
+def test_torch_compile_matches_eager_and_is_deterministic(qt_mod, cuda_device, layout, compile_backend, monkeypatch):
+    """torch.compile of a quantized model gives the eager-mode output (rtol/atol 1e-3) and the same
+    bits on every run (reference tests/test_integration.py:169-215).  The custom ops trace through
+    their fake kernels; under the compiler linear(x, w, b) arrives as t + addmm / mm."""
+    monkeypatch.setenv("CK_STRICT", "1")
+    torch._dynamo.reset()
+    model = _TwoLayerModel(qt_mod, layout, cuda_device)
+    x = torch.randn(16, 64, generator=torch.Generator(device="cpu").manual_seed(22)).bfloat16().to(cuda_device)
+    with torch.no_grad():
+        ref = model(x)
+        compiled = torch.compile(model, backend=compile_backend)
+        outs = [compiled(x).clone() for _ in range(3)]
+    assert outs[0].shape == ref.shape and outs[0].dtype == ref.dtype
+    torch.testing.assert_close(outs[0].float(), ref.float(), rtol=1e-3, atol=1e-3)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+def test_mm_of_compile_decomposition_hits_kernel(qt_mod, cuda_device, monkeypatch):
+    """mm(a, b.t()) - what torch.compile makes of linear(a, b) - runs the tensor-core kernel and meets
+    the GEMM contract against the oracle (reference tests/test_tensor.py:988-1008, there rtol 0.3)."""
+    monkeypatch.setenv("CK_STRICT", "1")
+    g = torch.Generator(device="cpu").manual_seed(23)
+    a = torch.randn(32, 64, generator=g).bfloat16().to(cuda_device)
+    b = torch.randn(128, 64, generator=g).bfloat16().to(cuda_device)
+    for layout in LAYOUTS:
+        qa = qt_mod.QuantizedTensor.from_float(a, layout)
+        qb = qt_mod.QuantizedTensor.from_float(b, layout)
+        got = torch.mm(qa, qb.t())
+        ref = _oracle_linear(layout, qa, qb, None).to(torch.bfloat16).float()
+        assert _rel(got.cpu(), ref) <= 1e-3
+
+
+# ------------------------------------------------------------------------------------------ error path
+def test_strict_mode_reports_a_kernel_wait_that_gave_up(qt_mod, cuda_device, monkeypatch):
+    """A launch returns 0 before its kernel runs; a bounded wait that gives up only sets a device
+    status word.  With CK_STRICT=1 the layouts read it after the call chain and raise.  The word is
+    set from the host here (no kernel is made to fail)."""
+    from comfy_kitchen.backends import cuda as backend
+
+    lib = backend.load_library()
+    g = torch.Generator(device="cpu").manual_seed(24)
+    x = qt_mod.QuantizedTensor.from_float(torch.randn(32, 64, generator=g).bfloat16().to(cuda_device), LAYOUTS[0])
+    w = qt_mod.QuantizedTensor.from_float(torch.randn(64, 64, generator=g).bfloat16().to(cuda_device), LAYOUTS[0])
+    backend.check_device_status("clean start")  # nothing pending
+    assert lib.ck_debug_set_gemm_status(1) == 0
+    with pytest.raises(RuntimeError, match="gave up"):
+        backend.check_device_status("test")
+    backend.check_device_status("cleared by the read")
+    monkeypatch.setenv("CK_STRICT", "1")
+    assert lib.ck_debug_set_gemm_status(1) == 0
+    with pytest.raises(RuntimeError, match="gave up"), torch.inference_mode():
+        F.linear(x, w)
+    monkeypatch.setenv("CK_STRICT", "0")
+    assert lib.ck_debug_set_gemm_status(1) == 0
+    with torch.inference_mode():
+        F.linear(x, w)  # not strict: the call chain does not look at the status word
+    with pytest.raises(RuntimeError, match="gave up"):
+        backend.check_device_status("explicit check")
