@@ -56,6 +56,33 @@ class _QuantizedLinearBase(nn.Module):
         else:
             self.register_parameter("bias", None)
 
+    def _target_device(self, incoming: torch.Tensor | None = None) -> torch.device:
+        """Where loaded tensors belong: next to the tensors this module holds now (it may have been
+        moved since construction), else the construction device; a module that holds nothing yet and
+        was built without a device follows the incoming tensor."""
+        for held in (self.bias, self.weight):
+            if isinstance(held, torch.Tensor):
+                return held.device
+        if self.device.type == "cpu" and incoming is not None and incoming.device.type != "cpu":
+            return incoming.device
+        return self.device
+
+    def _apply(self, fn, recurse=True):
+        out = super()._apply(fn, recurse)
+        for held in (self.bias, self.weight):
+            if isinstance(held, torch.Tensor):
+                self.device = held.device
+                break
+        return out
+
+    def _load_plain_entries(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs,
+                            handled: set) -> None:
+        """The bias (and whatever else nn.Module loads itself); ``handled`` keys are this class's own."""
+        before = len(missing_keys)
+        nn.Module._load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                                        error_msgs)
+        missing_keys[before:] = [k for k in missing_keys[before:] if k not in handled]
+
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, " \
                f"layout={self.layout_name}"
@@ -110,13 +137,18 @@ class NVFP4Linear(_QuantizedLinearBase):
 
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
         names = ["weight", "weight_scale", "weight_scale_2"]
+        handled = {prefix + "weight", prefix + "input_scale"}
         absent = [n for n in names if prefix + n not in state_dict]
         if absent:
+            # the quantized weight cannot be built; the bias is still loaded
             missing_keys.extend(prefix + n for n in absent)
+            self._load_plain_entries(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs,
+                                     handled | {prefix + n for n in names})
             return
-        codes = state_dict.pop(prefix + "weight").to(device=self.device)
-        block_scale = state_dict.pop(prefix + "weight_scale").to(device=self.device)
-        tensor_scale = state_dict.pop(prefix + "weight_scale_2").to(device=self.device)
+        device = self._target_device(state_dict[prefix + "weight"])
+        codes = state_dict.pop(prefix + "weight").to(device=device)
+        block_scale = state_dict.pop(prefix + "weight_scale").to(device=device)
+        tensor_scale = state_dict.pop(prefix + "weight_scale_2").to(device=device)
         sc_cols = (self.in_features // 16 + 3) // 4 * 4
         sc_rows = (self.out_features + 127) // 128 * 128
         if block_scale.numel() != sc_rows * sc_cols:
@@ -128,12 +160,9 @@ class NVFP4Linear(_QuantizedLinearBase):
         if input_scale is None:
             self.input_scale = None  # dynamic activation scale
         else:
-            self.input_scale = nn.Parameter(input_scale.to(device=self.device, dtype=torch.float32).reshape(()),
+            self.input_scale = nn.Parameter(input_scale.to(device=device, dtype=torch.float32).reshape(()),
                                             requires_grad=False)
-        before = len(missing_keys)
-        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
-        handled = {prefix + "weight", prefix + "input_scale"}
-        missing_keys[before:] = [k for k in missing_keys[before:] if k not in handled]
+        self._load_plain_entries(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs, handled)
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, input_scale: torch.Tensor | float | None = None) -> "NVFP4Linear":
@@ -163,9 +192,12 @@ class MXFP8Linear(_QuantizedLinearBase):
         absent = [n for n in names if prefix + n not in state_dict]
         if absent:
             missing_keys.extend(prefix + n for n in absent)
+            self._load_plain_entries(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs,
+                                     {prefix + n for n in names})
             return
-        data = state_dict.pop(prefix + "weight").to(device=self.device)
-        block_scale = state_dict.pop(prefix + "weight_scale").to(device=self.device)
+        device = self._target_device(state_dict[prefix + "weight"])
+        data = state_dict.pop(prefix + "weight").to(device=device)
+        block_scale = state_dict.pop(prefix + "weight_scale").to(device=device)
         sc_cols = (self.in_features // 32 + 3) // 4 * 4
         sc_rows = (self.out_features + 127) // 128 * 128
         if block_scale.numel() != sc_rows * sc_cols:
@@ -178,9 +210,8 @@ class MXFP8Linear(_QuantizedLinearBase):
                                               orig_dtype=self.compute_dtype,
                                               orig_shape=(self.out_features, self.in_features))
         self.weight = nn.Parameter(QuantizedTensor(data.contiguous(), MXFP8, params), requires_grad=False)
-        before = len(missing_keys)
-        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
-        missing_keys[before:] = [k for k in missing_keys[before:] if k != prefix + "weight"]
+        self._load_plain_entries(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs,
+                                 {prefix + "weight"})
 
     @classmethod
     def from_linear(cls, linear: nn.Linear) -> "MXFP8Linear":

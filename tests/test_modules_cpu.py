@@ -85,3 +85,32 @@ def test_patcher_rules_on_a_cpu_model():
     assert report["skipped"]["0"] == "weight is not on a CUDA device"  # quantization runs on the GPU only
     with pytest.raises(KeyError):
         patch_model(model, layout="int3")
+
+
+def test_load_follows_the_module_after_it_was_moved():
+    """A layer built on the CPU and moved afterwards loads its checkpoint onto the device it is on now
+    (the 'meta' device stands in for the GPU here), not the one it was built on."""
+    from comfy_kitchen.modules import MXFP8Linear, NVFP4Linear
+
+    layer = NVFP4Linear(256, 384).to("meta")
+    assert layer.device.type == "meta"
+    res = layer.load_state_dict(_fake_nvfp4_state(), strict=False, assign=False)
+    assert not [k for k in res.missing_keys if "bias" not in k]
+    assert layer.weight._qdata.device.type == "meta" and layer.weight._params.block_scale.device.type == "meta"
+    assert layer.input_scale.device.type == "meta"
+    layer8 = MXFP8Linear(256, 384).to("meta")
+    layer8.load_state_dict({"weight": torch.zeros(384, 256, dtype=torch.uint8),
+                            "weight_scale": torch.full((384 * 8,), 127, dtype=torch.uint8),
+                            "bias": torch.zeros(384, dtype=torch.bfloat16)})
+    assert layer8.weight._qdata.device.type == "meta"
+
+
+def test_bias_is_loaded_even_when_the_quantized_entries_are_missing():
+    from comfy_kitchen.modules import NVFP4Linear
+
+    layer = NVFP4Linear(256, 384)
+    with torch.no_grad():
+        layer.bias.zero_()
+    res = layer.load_state_dict({"bias": torch.ones(384, dtype=torch.bfloat16)}, strict=False)
+    assert set(res.missing_keys) == {"weight", "weight_scale", "weight_scale_2"}
+    assert bool((layer.bias == 1).all())

@@ -196,6 +196,29 @@ def test_dynamic_tensor_scale_matches_layout_expression(ck, cuda_device, dtype, 
         assert backend.nvfp4_tensor_scale(sl).cpu().view(torch.int32).item() == want_sl.view(torch.int32).item()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_dynamic_tensor_scale_against_the_device_evaluation_of_the_expression(ck, cuda_device, dtype):
+    """The kernel pins the IEEE division of the expression (what torch computes on the CPU).  torch's
+    CUDA kernel for ``tensor / python_scalar`` multiplies by a float32 reciprocal instead, which can land
+    one unit in the last place of x's dtype away: the two evaluations agree to that, and are usually
+    identical."""
+    from comfy_kitchen.backends import cuda as backend
+
+    same = 0
+    for seed in range(40):
+        g = torch.Generator(device="cpu").manual_seed(1000 + seed)
+        x = (torch.randn(64, 128, generator=g) * (0.1 + seed)).to(dtype)
+        xd = x.to(cuda_device)
+        got = backend.nvfp4_tensor_scale(xd)
+        dev = (torch.amax(xd.abs()) / (448.0 * 6.0)).to(torch.float32)
+        cpu = (torch.amax(x.abs()) / (448.0 * 6.0)).to(torch.float32)
+        assert got.cpu().view(torch.int32).item() == cpu.view(torch.int32).item()
+        step = torch.finfo(dtype).eps * abs(cpu.item())  # one unit in the last place of x's dtype, at most
+        assert abs(got.item() - dev.item()) <= step
+        same += int(got.item() == dev.item())
+    assert same >= 30
+
+
 def test_layout_uses_the_dynamic_scale_kernel(ck, cuda_device):
     from comfy_kitchen.tensor import QuantizedTensor
 
