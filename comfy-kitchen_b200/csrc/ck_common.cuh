@@ -90,6 +90,9 @@ __device__ __forceinline__ Vec256 ld_global_stream_256(const void* p) {
   return r;
 }
 
+// Ask L2 for the 128-byte line that holds *p (no data is returned, nothing is tracked).
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ void st_global_256(void* p, const Vec256& r) {
   asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.w[0]), "r"(r.w[1]),
                "r"(r.w[2]), "r"(r.w[3]), "r"(r.w[4]), "r"(r.w[5]), "r"(r.w[6]), "r"(r.w[7])

@@ -132,16 +132,10 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
 // merge with one shuffle, per-thread constants (tensor scale, its reciprocal) are set up
 // once, and a block of 32 x 8 threads walks row groups with a grid stride so that every SM
 // holds the same amount of work.
-#ifndef CK_Q_MINBLOCKS
-#define CK_Q_MINBLOCKS 2
-#endif
-#ifndef CK_Q_ROWS
-#define CK_Q_ROWS 16
-#endif
-constexpr int kPairRows = CK_Q_ROWS;  // rows per thread block; 32 lanes x 2 blocks x 16 = 1024 columns per warp
+constexpr int kPairRows = 16;  // rows per thread block; 32 lanes x 2 blocks x 16 = 1024 columns per warp
 
 template <typename T, bool kHiFirst>
-__global__ void __launch_bounds__(32 * kPairRows, CK_Q_MINBLOCKS)
+__global__ void __launch_bounds__(32 * kPairRows, 2)
 quantize_nvfp4_pair_kernel(const T* __restrict__ x, const float* __restrict__ global_scale,
                            uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int rows, int cols,
                            int rows_pad, int sc_pad, int row_groups) {
@@ -149,6 +143,17 @@ quantize_nvfp4_pair_kernel(const T* __restrict__ x, const float* __restrict__ gl
   const int pc = blockIdx.y * 32 + threadIdx.x;  // scale columns 2*pc and 2*pc + 1
   const bool has_data = pc < (cols >> 5);
   const bool has_scale = (threadIdx.x & 1) == 0 && 2 * pc < sc_pad;
+  // Ahead of the dependency wait: ask L2 for this block's first two row groups.  A prefetch only
+  // warms the cache (L2 is the point of coherence: what the previous kernel still writes is seen
+  // by the loads after the wait), and it takes the DRAM latency of the first loads off the
+  // critical path of a kernel that only runs for a few microseconds.
+  if (has_data && (threadIdx.x & 1) == 0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = (blockIdx.x + i * gridDim.x) * kPairRows + threadIdx.y;
+      if (row < rows) prefetch_l2(x + static_cast<int64_t>(row) * cols + pc * 32);  // one 128-byte line per lane pair
+    }
+  }
   pdl_wait();  // the tensor scale and x may come from the kernel before this one
   const TensorScale ts = make_tensor_scale(__ldg(global_scale));
   const int col_tiles = sc_pad >> 2;
@@ -216,10 +221,14 @@ __global__ void __launch_bounds__(kThreads)
 quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
                       int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols, int64_t sc_pad) {
   pdl_launch_dependents();
-  pdl_wait();
   const int64_t sc = blockIdx.y * kColsPerBlock + threadIdx.x;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + threadIdx.y;
   const int64_t n_sc = num_cols >> 5;
+  if constexpr (kVec) {
+    // ahead of the dependency wait: ask L2 for the thread pair's 128-byte line (warms the cache only)
+    if (row < num_rows && sc < n_sc && (threadIdx.x & 1) == 0) prefetch_l2(x + row * orig_cols + sc * 32);
+  }
+  pdl_wait();
   uint32_t scale_byte = 0;
   if (row < num_rows && sc < n_sc) {
     float lo[16], hi[16];

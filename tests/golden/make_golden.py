@@ -184,7 +184,7 @@ def main(ref_root: str) -> None:
     for name, d in out.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **d)
 
-    # ---------------- large case: BASELINE config 1 operands, digests only ------------------------
+    # ---------------- large case: the CPU-runnable linear (x [256,3072], W [3072,3072], seed 0), digests only ----
     g0 = torch.Generator(device="cpu").manual_seed(0)
     x = torch.randn(256, 3072, generator=g0).bfloat16()
     w = (torch.randn(3072, 3072, generator=g0) * 0.02).bfloat16()

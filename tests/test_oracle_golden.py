@@ -98,7 +98,7 @@ def test_gemm_mxfp8_contract(name):
 
 
 def test_large_case_digests():
-    """BASELINE config-1 operands ([256,3072] and [3072,3072], seed 0): digests of all four outputs."""
+    """Operands of the CPU-runnable linear ([256,3072] and [3072,3072], seed 0): digests of all four outputs."""
     import torch
 
     with open(os.path.join(GOLDEN_DIR, "large_digests.json")) as f:
