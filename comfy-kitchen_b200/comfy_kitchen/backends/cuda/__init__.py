@@ -308,8 +308,8 @@ _retired_workspaces: list = []  # outgrown buffers stay alive: a captured CUDA g
 def _gemm_workspace(lib, is_mxfp8: bool, m: int, n: int, k: int, device):
     """(pointer, bytes) of the split-K workspace for this shape on the current stream, or (None, 0).
 
-    The library decides (few output tiles, long K); the buffer is cached per device and stream
-    and only ever grows, so steady-state calls allocate nothing."""
+    The library decides (few activation rows, or few output tiles and a long K); the buffer is
+    cached per device and stream and only ever grows, so steady-state calls allocate nothing."""
     need = int(lib.ck_scaled_mm_workspace_bytes(int(is_mxfp8), m, n, k))
     if need == 0:
         return None, 0
@@ -318,7 +318,9 @@ def _gemm_workspace(lib, is_mxfp8: bool, m: int, n: int, k: int, device):
     if ws is None or ws.numel() < need:
         if ws is not None:
             _retired_workspaces.append(ws)
-        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        # zero-filled: the head of the workspace holds arrival counters that must start at zero
+        # (every call leaves them at zero again)
+        ws = torch.zeros(max(need, 1 << 22), dtype=torch.uint8, device=device)
         _gemm_workspaces[key] = ws
     return ws.data_ptr(), ws.numel()
 

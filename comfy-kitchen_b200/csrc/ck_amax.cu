@@ -57,8 +57,7 @@ __device__ __forceinline__ float abs_max_of_vec(const Vec256& raw) {
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-nvfp4_tensor_scale_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ scale_out,
-                          unsigned int* __restrict__ scratch) {
+nvfp4_tensor_scale_kernel(const T* x, int64_t n, float* scale_out, unsigned int* scratch) {
   constexpr int kPerVec = 32 / sizeof(T);  // elements per 256-bit load
   constexpr int kVecs = kElemsPerThread / kPerVec;
   pdl_launch_dependents();

@@ -36,6 +36,21 @@ __host__ __device__ constexpr int64_t ceil_div(int64_t x, int64_t m) { return (x
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Device address of the GEMM kernels' status word on the current device (ck_gemm.cu).
+int gemm_status_word(int** out);
+
+// Caller-owned GEMM workspace: the first kWorkspaceTicketBytes hold the arrival counters of the
+// small-M path (zero before the first use, left zero by every call); partial tiles of either
+// split-K path follow.
+constexpr int64_t kWorkspaceTicketBytes = 65536;
+
+// GEMMs with few activation rows (ck_gemm_smallm.cu).
+bool small_m_applies(int64_t M, int64_t N, int64_t K);
+int64_t small_m_workspace_bytes(bool is_mxfp8, int64_t M, int64_t N, int64_t K);
+int scaled_mm_small_m(bool is_mxfp8, const void* a, const void* b, const void* sfa, const void* sfb, const float* tsa,
+                      const float* tsb, const float* alpha, const void* bias, int bias_dtype, void* out, int out_dtype,
+                      int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, cudaStream_t stream);
+
 // ---- programmatic dependent launch ------------------------------------------------------
 // The streaming kernels and the GEMMs of this library are launched with programmatic stream
 // serialization: each kernel lets its successor start being scheduled at once
@@ -88,6 +103,17 @@ __device__ __forceinline__ Vec256 ld_global_stream_256(const void* p) {
                  "=r"(r.w[6]), "=r"(r.w[7])
                : "l"(p));
   return r;
+}
+
+// Scalar read of a value the previous kernel in the stream may have produced (a tensor scale,
+// alpha).  Kernels launched with programmatic stream serialization start before their predecessor
+// has finished; a read-only-cache load (__ldg, or what the compiler makes of a const __restrict__
+// pointer) is "invariant" to the compiler, which may then hoist it above griddepcontrol.wait and
+// read the value of the launch before.  This is an ordinary coherent load that stays where it is.
+__device__ __forceinline__ float ld_f32_dependent(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
 }
 
 // Ask L2 for the 128-byte line that holds *p (no data is returned, nothing is tracked).

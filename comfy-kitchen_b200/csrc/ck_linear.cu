@@ -11,18 +11,21 @@ namespace ck {
 namespace {
 
 struct FromFloatLayout {
-  int64_t codes_off, scales_off, scale_off, scratch_off, total;
+  int64_t scratch_off, scale_off, codes_off, scales_off, total;
 };
 
-// Workspace layout: codes [M, K/2] | tiled block scales | dynamic tensor scale | tensor-scale scratch,
-// every part on a 256-byte boundary.
-FromFloatLayout from_float_layout(int64_t M, int64_t K, bool dynamic_scale) {
+// Workspace layout: tensor-scale scratch | dynamic tensor scale | codes [M, K/2] | tiled block scales.
+// The scratch comes first and has a fixed size: it must read as zero at the start of every call, and
+// only a region that no other part of any shape's layout ever overlaps stays that way.
+constexpr int64_t kScaleScratchBytes = 256 * 1024;  // covers 2^30 elements
+
+FromFloatLayout from_float_layout(int64_t M, int64_t K) {
   FromFloatLayout l{};
-  l.codes_off = 0;
-  l.scales_off = round_up(M * (K / 2), 256);
-  l.scale_off = l.scales_off + round_up(round_up(M, 128) * round_up(K / 16, 4), 256);
-  l.scratch_off = l.scale_off + 256;
-  l.total = l.scratch_off + (dynamic_scale ? round_up(ck_nvfp4_tensor_scale_scratch_bytes(M * K), 256) : 0);
+  l.scratch_off = 0;
+  l.scale_off = kScaleScratchBytes;
+  l.codes_off = l.scale_off + 256;
+  l.scales_off = l.codes_off + round_up(M * (K / 2), 256);
+  l.total = l.scales_off + round_up(round_up(M, 128) * round_up(K / 16, 4), 256);
   return l;
 }
 
@@ -31,7 +34,8 @@ FromFloatLayout from_float_layout(int64_t M, int64_t K, bool dynamic_scale) {
 
 extern "C" int64_t ck_linear_nvfp4_from_float_workspace_bytes(int64_t M, int64_t K, int dynamic_scale) {
   if (M <= 0 || K <= 0 || K % 32 != 0 || M >= (1ll << 30) || K >= (1ll << 30)) return 0;
-  return ck::from_float_layout(M, K, dynamic_scale != 0).total;
+  if (dynamic_scale != 0 && ck_nvfp4_tensor_scale_scratch_bytes(M * K) > ck::kScaleScratchBytes) return 0;
+  return ck::from_float_layout(M, K).total;
 }
 
 extern "C" int ck_linear_nvfp4_from_float(const void* x, int x_dtype, const float* x_scale, const void* w_codes,
@@ -44,7 +48,10 @@ extern "C" int ck_linear_nvfp4_from_float(const void* x, int x_dtype, const floa
   CK_REQUIRE(K % 32 == 0, "linear_nvfp4_from_float: K=%lld must be a multiple of 32", (long long)K);
   CK_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "linear_nvfp4_from_float: workspace must be 256-byte aligned");
   const bool dynamic = x_scale == nullptr;
-  const FromFloatLayout l = from_float_layout(M, K, dynamic);
+  CK_REQUIRE(!dynamic || ck_nvfp4_tensor_scale_scratch_bytes(M * K) <= kScaleScratchBytes,
+             "linear_nvfp4_from_float: %lld x %lld elements are too many for the dynamic scale of this entry point",
+             (long long)M, (long long)K);
+  const FromFloatLayout l = from_float_layout(M, K);
   CK_REQUIRE(workspace_bytes >= l.total, "linear_nvfp4_from_float: workspace of %lld bytes, %lld needed",
              (long long)workspace_bytes, (long long)l.total);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -53,7 +60,7 @@ extern "C" int ck_linear_nvfp4_from_float(const void* x, int x_dtype, const floa
   const float* scale = x_scale;
   if (dynamic) {
     float* dyn = reinterpret_cast<float*>(ws + l.scale_off);
-    if (int rc = ck_nvfp4_tensor_scale(x, x_dtype, M * K, dyn, ws + l.scratch_off, l.total - l.scratch_off, stream)) return rc;
+    if (int rc = ck_nvfp4_tensor_scale(x, x_dtype, M * K, dyn, ws + l.scratch_off, kScaleScratchBytes, stream)) return rc;
     scale = dyn;
   }
   if (int rc = ck_quantize_nvfp4(x, x_dtype, scale, codes, scales, M, K, M, K, /*hi_first=*/1, stream)) return rc;

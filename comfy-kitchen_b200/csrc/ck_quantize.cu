@@ -102,7 +102,7 @@ __device__ __forceinline__ void store_scale_quad(uint8_t* scales, int64_t row, i
 // row, so aligned lane quads share a row and a 4-byte scale group.
 template <typename T, bool kVec, bool kFastDiv>
 __global__ void __launch_bounds__(kThreads)
-quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_scale, uint8_t* __restrict__ codes,
+quantize_nvfp4_kernel(const T* x, const float* global_scale, uint8_t* __restrict__ codes,
                       uint8_t* __restrict__ scales, int64_t orig_rows, int64_t orig_cols, int64_t num_rows,
                       int64_t num_cols, int64_t sc_pad, int hi_first) {
   pdl_launch_dependents();
@@ -118,7 +118,7 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
     } else {
       load16_guarded(x, row, sc * 16, orig_rows, orig_cols, v);
     }
-    const float g = __ldg(global_scale);
+    const float g = ld_f32_dependent(global_scale);
     uint32_t lo, hi;
     nvfp4_block<kFastDiv>(v, g, hi_first != 0, lo, hi, scale_byte);
     *reinterpret_cast<uint2*>(codes + row * (num_cols >> 1) + sc * 8) = make_uint2(lo, hi);
@@ -136,7 +136,7 @@ constexpr int kPairRows = 16;  // rows per thread block; 32 lanes x 2 blocks x 1
 
 template <typename T, bool kHiFirst>
 __global__ void __launch_bounds__(32 * kPairRows, 2)
-quantize_nvfp4_pair_kernel(const T* __restrict__ x, const float* __restrict__ global_scale,
+quantize_nvfp4_pair_kernel(const T* x, const float* global_scale,
                            uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int rows, int cols,
                            int rows_pad, int sc_pad, int row_groups) {
   pdl_launch_dependents();
@@ -155,7 +155,7 @@ quantize_nvfp4_pair_kernel(const T* __restrict__ x, const float* __restrict__ gl
     }
   }
   pdl_wait();  // the tensor scale and x may come from the kernel before this one
-  const TensorScale ts = make_tensor_scale(__ldg(global_scale));
+  const TensorScale ts = make_tensor_scale(ld_f32_dependent(global_scale));
   const int col_tiles = sc_pad >> 2;
   const int code_pitch = cols >> 1;
   // The loads of the next row group are issued before the arithmetic of the current one, so
@@ -218,7 +218,7 @@ __device__ __forceinline__ uint32_t e8m0_ceil_exponent(float r) {
 
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads)
-quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
+quantize_mxfp8_kernel(const T* x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
                       int64_t orig_rows, int64_t orig_cols, int64_t num_rows, int64_t num_cols, int64_t sc_pad) {
   pdl_launch_dependents();
   const int64_t sc = blockIdx.y * kColsPerBlock + threadIdx.x;

@@ -205,10 +205,11 @@ CK_API int ck_linear_nvfp4_fused(const void* a, const void* b, const void* sfa, 
  * back on `stream` and chained with programmatic dependent launch; results are bit-identical to
  * calling ck_nvfp4_tensor_scale, ck_quantize_nvfp4 and ck_scaled_mm_nvfp4 one after the other.
  * The quantized activation is written to `workspace` (device memory, 256-byte aligned, at least
- * ck_linear_nvfp4_from_float_workspace_bytes(M, K, x_scale == NULL) bytes; codes at offset 0).
- * With a dynamic scale the workspace must have been zero-filled once before its first use (the
- * scale kernel's scratch lives in it and is left zeroed by every call); calls that can overlap
- * on the GPU need separate workspaces.  K % 32 == 0, N % 8 == 0.
+ * ck_linear_nvfp4_from_float_workspace_bytes(M, K, x_scale == NULL) bytes; 0 = this shape is not
+ * supported).  The first 256 KiB of the workspace are the scale kernel's scratch: they must have
+ * been zero-filled once before the first call with a dynamic scale and are left zeroed by every
+ * call, whatever the shapes of the calls that share the workspace; calls that can overlap on the
+ * GPU need separate workspaces.  K % 32 == 0, N % 8 == 0; with a dynamic scale M x K <= 2^30.
  * Replaces the sequence QuantizedTensor.from_float -> F.linear of the reference
  * (comfy_kitchen/tensor/nvfp4.py:51-82 followed by tensor/nvfp4.py:214-264; the caller side is
  * samples/nvfp4_linear.py:77-80).

@@ -142,13 +142,16 @@ def test_mxfp8_matches_oracle(ck, cuda_device, shape):
     _check_mxfp8(ck, cuda_device, a, b, bias, torch.float32)
 
 
-@pytest.mark.parametrize("config", [1, 3, 4, 7])
+@pytest.mark.parametrize("config", [1, 3, 4, 7, 9])
 @pytest.mark.parametrize("shape", [(128, 128, 256), (384, 392, 288), (129, 264, 320), (1024, 768, 1024), (48, 136, 192), (2048, 1160, 512)])
 def test_every_kernel_configuration(ck, cuda_device, config, shape, monkeypatch):
-    """Each tile configuration (CK_GEMM_CONFIG: 64/128/256-wide single-CTA tiles and 256x256
-    CTA-pair tiles) on shapes with ragged M, N and K, including a CTA pair whose second CTA is past M."""
+    """Each tile configuration (CK_GEMM_CONFIG: 64/128/256-wide single-CTA tiles, 256x256 CTA-pair
+    tiles, 9 = the swapped-operand weight-streaming path) on shapes with ragged M, N and K, including
+    a CTA pair whose second CTA is past M."""
     monkeypatch.setenv("CK_GEMM_CONFIG", str(config))
     m, n, k = shape
+    if config == 9 and m > 32:
+        pytest.skip("configuration 9 is the weight-streaming path for at most 32 activation rows")
     a, b, bias = _operands(m, n, k, seed=config * 1000 + m + n + k)
     _check_nvfp4(ck, cuda_device, a, b, bias, torch.float32)
     _check_mxfp8(ck, cuda_device, a, b, bias, torch.bfloat16)
