@@ -241,10 +241,12 @@ CK_API int ck_scaled_mm_mxfp8(const void* a, const void* b, const void* sfa, con
  * cuBLASLt call a workspace the same way, comfy_kitchen/backends/cuda/__init__.py:117-124,
  * ops/cublas_gemm_nvfp4.cu:297-311).  ck_scaled_mm_workspace_bytes says how many bytes the
  * library would use for this shape: non-zero only for problems with few output tiles and a long
- * K (small M), which are then computed split-K - partial fp32 tiles in the workspace, a second
- * kernel adds them in a fixed order (deterministic) and applies alpha and bias.  With a null or
- * too small workspace the calls behave exactly like ck_scaled_mm_nvfp4 / ck_scaled_mm_mxfp8.
- * The workspace must be 16-byte aligned and must not be shared by calls that can overlap.
+ * K (small M), which are then computed split-K - partial fp32 tiles in the workspace, added in a
+ * fixed order (deterministic) either by a second kernel or, for at most 32 activation rows, by
+ * the warp that finishes a tile last.  With a null or too small workspace the calls behave
+ * exactly like ck_scaled_mm_nvfp4 / ck_scaled_mm_mxfp8.  The workspace must be 16-byte aligned,
+ * must have been zero-filled once before its first use (its first 64 KiB hold arrival counters
+ * that every call leaves at zero) and must not be shared by calls that can overlap.
  */
 CK_API int64_t ck_scaled_mm_workspace_bytes(int is_mxfp8, int64_t M, int64_t N, int64_t K);
 CK_API int ck_scaled_mm_nvfp4_ws(const void* a, const void* b, const void* block_scale_a,
