@@ -114,3 +114,25 @@ def test_bias_is_loaded_even_when_the_quantized_entries_are_missing():
     res = layer.load_state_dict({"bias": torch.ones(384, dtype=torch.bfloat16)}, strict=False)
     assert set(res.missing_keys) == {"weight", "weight_scale", "weight_scale_2"}
     assert bool((layer.bias == 1).all())
+
+
+def test_checkpoint_quantizer_selects_the_linear_weights(tmp_path, capsys):
+    """The offline quantizer's selection rules and its dry run (no GPU involved)."""
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "comfy-kitchen_b200", "quantize_checkpoint.py")
+    spec = importlib.util.spec_from_file_location("quantize_checkpoint", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sd = {"blk.fc1.weight": torch.zeros(256, 128), "blk.fc1.bias": torch.zeros(256), "blk.norm.weight": torch.zeros(128),
+          "head.weight": torch.zeros(16, 128), "odd.weight": torch.zeros(128, 72), "emb.weight": torch.zeros(1000, 128, dtype=torch.bfloat16)}
+    assert mod.select_keys(sd, 16, 64, [], None) == ["blk.fc1.weight", "emb.weight"]
+    assert mod.select_keys(sd, 32, 64, ["emb"], None) == ["blk.fc1.weight"]
+    assert mod.select_keys(sd, 16, 64, [], ["head.weight"]) == ["head.weight"]
+    with pytest.raises(KeyError):
+        mod.select_keys(sd, 16, 64, [], ["nope"])
+    ckpt = tmp_path / "m.pt"
+    torch.save({"state_dict": sd, "step": 3}, ckpt)
+    assert mod.main([str(ckpt), "--dry-run"]) == 0
+    assert "2 of 6 entries -> nvfp4" in capsys.readouterr().out

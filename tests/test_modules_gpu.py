@@ -184,3 +184,62 @@ def test_mmdit_shaped_stack_runs_quantized(ck, cuda_device):
     assert all(isinstance(m, NVFP4Linear) for m in quant.modules() if hasattr(m, "in_features"))
     rel = ((a.float() - b.float()).norm() / a.float().norm()).item()
     assert rel < 0.3
+
+
+def test_checkpoint_quantizer_cli_round_trip(ck, cuda_device, tmp_path):
+    """quantize_checkpoint.py on a saved dense model: the output loads into the quantized layers and
+    gives the result of quantizing the live layer."""
+    import importlib.util
+    import os
+
+    from comfy_kitchen.modules import NVFP4Linear
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "comfy-kitchen_b200", "quantize_checkpoint.py")
+    spec = importlib.util.spec_from_file_location("quantize_checkpoint", path)
+    cli = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cli)
+    lin = _dense(cuda_device)
+    src, dst = tmp_path / "dense.pt", tmp_path / "q.pt"
+    torch.save({k: v.cpu() for k, v in lin.state_dict().items()}, src)
+    assert cli.main([str(src), str(dst), "--layout", "nvfp4", "--device", str(cuda_device)]) == 0
+    sd = torch.load(dst, map_location="cpu", weights_only=True)
+    assert set(sd) == {"weight", "weight_scale", "weight_scale_2", "bias"} and sd["weight"].dtype == torch.uint8
+    layer = NVFP4Linear(256, 384, device=cuda_device)
+    layer.load_state_dict(sd)
+    x = torch.randn(64, 256, device=cuda_device, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        assert torch.equal(layer(x), NVFP4Linear.from_linear(lin)(x))
+
+
+def test_captured_graph_survives_growth_of_the_cached_scratch_buffers(ck, cuda_device):
+    """The wrappers cache scratch / workspace buffers per stream and replace them when a larger input
+    comes along; a CUDA graph captured before still points at the old buffer, which therefore has to
+    stay alive (and zeroed where the kernels expect zeros)."""
+    from comfy_kitchen.backends import cuda as backend
+    from comfy_kitchen.tensor import QuantizedTensor
+
+    side = torch.cuda.Stream()
+    x = torch.randn(64, 256, device=cuda_device, dtype=torch.bfloat16)
+    w = QuantizedTensor.from_float(torch.randn(128, 256, device=cuda_device, dtype=torch.bfloat16), "TensorCoreNVFP4Layout")
+    with torch.cuda.stream(side), torch.inference_mode():
+        key = (cuda_device, side.cuda_stream)
+        backend._scale_scratch.pop(key, None)
+        backend._scale_scratch[key] = torch.zeros(64, dtype=torch.uint8, device=cuda_device)  # small on purpose
+
+        def step():
+            return torch.nn.functional.linear(QuantizedTensor.from_float(x, "TensorCoreNVFP4Layout"), w)
+
+        eager = step()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            y = step()
+        old = backend._scale_scratch[key]
+        # a much larger input on the same stream outgrows the cached scratch
+        big = torch.randn(4096, 8192, device=cuda_device, dtype=torch.bfloat16)
+        backend.nvfp4_tensor_scale(big)
+        assert backend._scale_scratch[key] is not old and any(t is old for t in backend._retired_workspaces)
+        for _ in range(2):
+            graph.replay()
+            side.synchronize()
+            assert torch.equal(y, eager)
