@@ -187,6 +187,20 @@ def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor
 _scale_scratch: dict = {}
 
 
+def _scale_scratch_for(device, stream: int, need: int) -> torch.Tensor:
+    """The zeroed scratch buffer of the tensor-scale kernel for this device and stream, at least
+    ``need`` bytes.  An outgrown buffer is kept alive: a captured CUDA graph may still point at it."""
+    key = (device, stream)
+    scratch = _scale_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        if scratch is not None:
+            _retired_workspaces.append(scratch)
+        # 1 MiB covers 2^33 elements: growth (an allocation and a memset) is a first-call event
+        scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _scale_scratch[key] = scratch
+    return scratch
+
+
 def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
     """0-d float32 tensor ``amax(|x|) / (448 * 6)`` (division in x's dtype), computed by one kernel.
 
@@ -199,15 +213,7 @@ def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
     assert x.is_contiguous(), "Input tensor must be contiguous"
     n = x.numel()
     stream = _stream(x.device)
-    need = lib.ck_nvfp4_tensor_scale_scratch_bytes(n)
-    key = (x.device, stream)
-    scratch = _scale_scratch.get(key)
-    if scratch is None or scratch.numel() < need:
-        if scratch is not None:
-            _retired_workspaces.append(scratch)  # a captured CUDA graph may still point at it
-        # 1 MiB covers 2^33 elements: growth (an allocation and a memset) is a first-call event
-        scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
-        _scale_scratch[key] = scratch
+    scratch = _scale_scratch_for(x.device, stream, lib.ck_nvfp4_tensor_scale_scratch_bytes(n))
     out = torch.empty((), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         _check(lib.ck_nvfp4_tensor_scale(_ptr(x), DTYPE_TO_CODE[x.dtype], n, _ptr(out), _ptr(scratch), scratch.numel(),

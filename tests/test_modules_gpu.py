@@ -223,8 +223,6 @@ def test_captured_graph_survives_growth_of_the_cached_scratch_buffers(ck, cuda_d
     w = QuantizedTensor.from_float(torch.randn(128, 256, device=cuda_device, dtype=torch.bfloat16), "TensorCoreNVFP4Layout")
     with torch.cuda.stream(side), torch.inference_mode():
         key = (cuda_device, side.cuda_stream)
-        backend._scale_scratch.pop(key, None)
-        backend._scale_scratch[key] = torch.zeros(64, dtype=torch.uint8, device=cuda_device)  # small on purpose
 
         def step():
             return torch.nn.functional.linear(QuantizedTensor.from_float(x, "TensorCoreNVFP4Layout"), w)
@@ -235,10 +233,10 @@ def test_captured_graph_survives_growth_of_the_cached_scratch_buffers(ck, cuda_d
         with torch.cuda.graph(graph, stream=side):
             y = step()
         old = backend._scale_scratch[key]
-        # a much larger input on the same stream outgrows the cached scratch
-        big = torch.randn(4096, 8192, device=cuda_device, dtype=torch.bfloat16)
-        backend.nvfp4_tensor_scale(big)
+        # a request beyond the cached size replaces the buffer; the captured graph keeps using the old one
+        backend._scale_scratch_for(cuda_device, side.cuda_stream, old.numel() * 2)
         assert backend._scale_scratch[key] is not old and any(t is old for t in backend._retired_workspaces)
+        torch.nn.functional.linear(QuantizedTensor.from_float(x * 2, "TensorCoreNVFP4Layout"), w)  # uses the new buffer
         for _ in range(2):
             graph.replay()
             side.synchronize()
