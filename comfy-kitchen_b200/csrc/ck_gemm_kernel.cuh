@@ -8,19 +8,18 @@
 //   warp 0    TMA producer: per pipeline stage one 128-row x 128-byte box of A, one box of B
 //             (128-byte swizzle) and the matching 512-byte scale tiles (linear bulk copies, or
 //             3-D tensor maps in a pair) into a STAGES-deep shared-memory ring.
-//   warp 1    MMA issuer: four tcgen05.mma per stage (32 bytes of K each) into a fp32
-//             accumulator in tensor memory; releases the stage / publishes the accumulator with
-//             tcgen05.commit.  Nothing else: the issue slot of this warp is the resource that
-//             decides whether the tensor pipe stays busy.
+//   warp 1    MMA issuer: per landed stage, copies the stage's scale tiles shared -> tensor
+//             memory (tcgen05.cp, up to 12) and issues four tcgen05.mma (32 bytes of K each) into
+//             a fp32 accumulator in tensor memory; releases the stage / publishes the accumulator
+//             with tcgen05.commit.  The tensor-memory scale columns are buffered per stage like
+//             the ring.  (Scale copies on a warp of their own were measured: the extra barrier
+//             hop between landing and issue costs 3-15 % at every shape.)
 //   warps 2.. epilogue (8 warps; 16 for the fused epilogue, 4 for 64-wide tiles): tcgen05.ld
 //             the accumulator into registers, hand it back at once, then alpha * acc + bias,
 //             convert, stage the rows in swizzled shared memory and write them with TMA stores
-//             while the next tile computes The fused variant applies GELU and
+//             while the next tile computes.  The fused variant applies GELU and
 //             re-quantizes to NVFP4 instead; split-K items store raw fp32 partial tiles to a
 //             workspace; the all-gather variant stores every tile into all ranks' results.
-//   last warp scale copier: copies each landed stage's scale tiles shared -> tensor memory
-//             (tcgen05.cp, up to 12 per stage) and tells the MMA warp through a barrier of
-//             its own.  The tensor-memory scale columns are buffered per stage like the ring.
 // With NUM_ACC == 2 the epilogue of tile i overlaps the main loop of tile i+1 entirely.
 //
 // All synchronisation is by mbarriers with bounded waits (ck_sm100.cuh): a protocol error
@@ -38,6 +37,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 namespace ck {
 namespace {
@@ -55,7 +55,7 @@ constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
 // element and must keep up with the tensor pipe), one for a 64-wide tile.
 constexpr int epilogue_warps(bool fused, int tile_n) { return (fused && tile_n >= 256) ? 16 : (tile_n <= 64) ? 4 : 8; }
 constexpr int num_threads(bool fused, int tile_n) {
-  return 96 + 32 * epilogue_warps(fused, tile_n);  // + TMA, MMA and scale-copy warps
+  return 64 + 32 * epilogue_warps(fused, tile_n);  // + TMA and MMA warps
 }
 constexpr int pow2_at_least(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
 
@@ -332,7 +332,6 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   static_assert(!(FUSED && OUT_STAGE != 0), "the fused epilogue stores from registers");
   static_assert(!SWAP || (!FUSED && OUT_STAGE == 0 && CTAS == 1), "swapped operands: plain epilogue, one CTA");
   constexpr int kNumEpilogueWarps = epilogue_warps(FUSED, TILE_N);
-  constexpr int kScaleWarp = 2 + kNumEpilogueWarps;
   constexpr int kThreads = num_threads(FUSED, TILE_N);
   static_assert(TILE_N <= 32 * kNumEpilogueWarps, "one bias value per epilogue thread");
   // Everything the kernel does until a role's griddepcontrol.wait is independent of the kernel
@@ -352,14 +351,13 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem_out = smem + Cfg::kRingBytes;  // 1024-byte aligned (swizzled store boxes)
   float* smem_bias = reinterpret_cast<float*>(smem_out + Cfg::kOutStageBytes);  // [3][TILE_N]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bias + 3 * TILE_N);
-  uint64_t* full_bar = bars;                       // [STAGES] producer -> scale copier (operands and scales landed)
+  uint64_t* full_bar = bars;                       // [STAGES] producer -> MMA (operands and scales landed)
   uint64_t* empty_bar = bars + STAGES;             // [STAGES] MMA -> producer (stage and its scale columns free)
-  uint64_t* sf_full_bar = bars + 2 * STAGES;       // [STAGES] scale copier -> MMA (scales in tensor memory)
-  uint64_t* acc_full_bar = bars + 3 * STAGES;      // [NUM_ACC] MMA -> epilogue
+  uint64_t* acc_full_bar = bars + 2 * STAGES;      // [NUM_ACC] MMA -> epilogue
   uint64_t* acc_empty_bar = acc_full_bar + NUM_ACC;  // [NUM_ACC] epilogue -> MMA
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + NUM_ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  static_assert((3 * STAGES + 2 * NUM_ACC) * 8 + 8 <= 256, "barrier area");
+  static_assert((2 * STAGES + 2 * NUM_ACC) * 8 + 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -377,7 +375,6 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int s = 0; s < STAGES; ++s) {
         mbar_init(&full_bar[s], 1);
         mbar_init(&empty_bar[s], 1);
-        mbar_init(&sf_full_bar[s], 1);
       }
       for (int a = 0; a < NUM_ACC; ++a) {
         mbar_init(&acc_full_bar[a], 1);
@@ -496,53 +493,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         __syncwarp();
       }
     }
-  } else if ((warp == 1 || warp == kScaleWarp) && cta_rank != 0) {
+  } else if (warp == 1 && cta_rank != 0) {
     // second CTA of a pair: the leader issues the MMAs and the scale copies for both
-  } else if (warp == kScaleWarp) {
-    // ------------------------------------------------------------------ scale copier
-    const uint32_t sfa_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfa)));
-    const uint32_t sfb_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfb)));
-    const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
-    const uint32_t t_sfa0 = tmem_base + Cfg::kSfaCol;
-    const uint32_t t_sfb0 = tmem_base + Cfg::kSfbCol;
-    const uint32_t sf_full_addr = smem_u32(sf_full_bar);
-    int ring_s = 0;
-    uint32_t ring_ph = 0;
-    for (int item = worker; item < num_items; item += num_workers) {
-      const int tile = item / splits;
-      const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
-      const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
-      for (int ks = ks_begin; ks < ks_end; ++ks) {
-        const int s = ring_s;
-        const uint32_t ph = ring_ph;
-        if (++ring_s == STAGES) {
-          ring_s = 0;
-          ring_ph ^= 1u;
-        }
-        // The previous round's MMAs on this stage have retired: the producer refilled the
-        // slot only after the stage's "empty" barrier, which their commit signalled.
-        mbar_wait(&full_bar[s], ph, abort_flag);
-        tc_fence_after_sync();
-        if (elect_one()) {
-          const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
-          const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
-          const uint32_t t_sfa = t_sfa0 + s * Cfg::kSfColsPerBuf;
-          const uint32_t t_sfb = t_sfb0 + s * Cfg::kSfColsPerBuf;
-          // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units)
-#pragma unroll
-          for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
-            tc_copy_scales_32x128b<CTAS>(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
-#pragma unroll
-            for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
-              tc_copy_scales_32x128b<CTAS>(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
-                                           desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
-            }
-          }
-          tc_commit<CTAS>(sf_full_addr + s * 8);
-        }
-        __syncwarp();
-      }
-    }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // Descriptors differ between stages only in their start-address field, so the loop
@@ -550,6 +502,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t a_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_a)));
     const uint32_t b_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_b)));
     const uint32_t op_hi = static_cast<uint32_t>(make_operand_desc_sw128(0) >> 32);
+    const uint32_t sfa_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfa)));
+    const uint32_t sfb_lo0 = static_cast<uint32_t>(make_scale_desc(smem_u32(smem_sfb)));
+    const uint32_t sf_hi = static_cast<uint32_t>(make_scale_desc(0) >> 32);
     const uint32_t t_sfa0 = tmem_base + Cfg::kSfaCol;
     const uint32_t t_sfb0 = tmem_base + Cfg::kSfbCol;
     const uint32_t empty_addr = smem_u32(empty_bar);
@@ -578,9 +533,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           ring_ph ^= 1u;
         }
         CK_TRACE2(1, it);
-        // Scales of the stage are in tensor memory; the copier waited for the stage's loads
-        // before it issued them, so the operands have landed too.
-        mbar_wait(&sf_full_bar[s], ph, abort_flag);
+        mbar_wait(&full_bar[s], ph, abort_flag);
         if (ks == ks_begin) CK_TRACE(2);
         if (ks == ks_end - 1) CK_TRACE(3);
         CK_TRACE2(2, it);
@@ -591,6 +544,20 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const int n_mma = min(kMmaPerStage, total_mma - ks * kMmaPerStage);
           const uint32_t t_sfa = t_sfa0 + s * Cfg::kSfColsPerBuf;
           const uint32_t t_sfb_tile = t_sfb0 + s * Cfg::kSfColsPerBuf + sfb_shift;
+          // scale tiles of this stage: shared -> tensor memory (512 bytes = 32 descriptor units);
+          // the tensor pipe runs them in order ahead of the MMAs that read them
+          const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4);
+          const uint32_t sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
+          const uint32_t t_sfb = t_sfb0 + s * Cfg::kSfColsPerBuf;
+#pragma unroll
+          for (int t = 0; t < Cfg::kSfTilesPerStage; ++t) {
+            tc_copy_scales_32x128b<CTAS>(t_sfa + t * 4, desc64(sfa_lo + t * 32, sf_hi));
+#pragma unroll
+            for (int r = 0; r < Cfg::kSfbRowBlocks; ++r) {
+              tc_copy_scales_32x128b<CTAS>(t_sfb + t * Cfg::kSfbColsPerTile + r * 4,
+                                           desc64(sfb_lo + (r * Cfg::kSfTilesPerStage + t) * 32, sf_hi));
+            }
+          }
           if (ks == ks_begin) {
             // Only now does the tile need its accumulator: the wait for the epilogue to have
             // drained it comes after the first stage has landed.
@@ -1071,8 +1038,42 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Tensor maps are a pure function of (address, extents, box): a small per-thread table keeps the
+// ones of recent calls, so that a layer called again with the same buffers pays no encode.
+struct MapKey {
+  int tag;
+  const void* base;
+  int64_t d0, d1, d2, d3;
+  bool operator==(const MapKey& o) const {
+    return tag == o.tag && base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && d3 == o.d3;
+  }
+};
+
+template <typename Encode>
+int cached_map(CUtensorMap* map, const MapKey& key, Encode&& encode) {
+  struct Entry {
+    MapKey key;
+    CUtensorMap map;
+    bool valid;
+  };
+  constexpr int kEntries = 128;
+  thread_local std::vector<Entry> table(kEntries);  // on the heap: keeps the library's TLS block small
+  uint64_t h = reinterpret_cast<uintptr_t>(key.base) >> 8;
+  h = (h ^ (h >> 17) ^ static_cast<uint64_t>(key.tag) * 0x9E3779B97F4A7C15ull ^ static_cast<uint64_t>(key.d1) * 0xC2B2AE3D27D4EB4Full);
+  Entry& e = table[(h ^ (h >> 29)) % kEntries];
+  if (e.valid && e.key == key) {
+    *map = e.map;
+    return CK_OK;
+  }
+  if (int rc = encode(map)) return rc;
+  e.key = key;
+  e.map = *map;
+  e.valid = true;
+  return CK_OK;
+}
+
 // Row-major [rows, row_bytes] byte matrix, boxes of 128 bytes x box_rows rows, 128-byte swizzle.
-int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
@@ -1088,7 +1089,7 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
 
 // Scale tensor in the tiled layout as a 3-D array {128 x uint32 (one 512-byte tile), column
 // tile, row block}; a box is `tiles` consecutive column tiles of one row block.
-int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64_t col_tiles, int tiles) {
+int encode_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64_t col_tiles, int tiles) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(col_tiles), static_cast<cuuint64_t>(row_blocks)};
@@ -1104,7 +1105,7 @@ int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64
 
 // Row-major [rows, cols] output of `elem_bytes`-wide elements: boxes of 32 rows x 128 bytes,
 // 128-byte swizzle (the layout the epilogue stages its rows in).
-int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes, int64_t pitch_elems) {
+int encode_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes, int64_t pitch_elems) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const CUtensorMapDataType type = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
@@ -1116,6 +1117,21 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, in
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(CK_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", static_cast<int>(r));
   return CK_OK;
+}
+
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+  return cached_map(map, MapKey{0, base, rows, row_bytes, box_rows, 0},
+                    [&](CUtensorMap* m) { return encode_operand_map(m, base, rows, row_bytes, box_rows); });
+}
+
+int make_scale_map(CUtensorMap* map, const void* base, int64_t row_blocks, int64_t col_tiles, int tiles) {
+  return cached_map(map, MapKey{1, base, row_blocks, col_tiles, tiles, 0},
+                    [&](CUtensorMap* m) { return encode_scale_map(m, base, row_blocks, col_tiles, tiles); });
+}
+
+int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes, int64_t pitch_elems) {
+  return cached_map(map, MapKey{2, base, rows, cols, elem_bytes, pitch_elems},
+                    [&](CUtensorMap* m) { return encode_output_map(m, base, rows, cols, elem_bytes, pitch_elems); });
 }
 
 // Where the output goes (host side): `n` buffers (1 = plain GEMM), each holding this GEMM's
@@ -1195,10 +1211,17 @@ int launch_config(const Operands& ops, GemmParams p, const OutputSpec& os, cudaS
   p.out_tma = 0;
   p.n_out = 1;
   if constexpr (OUT_STAGE != 0) {
-    // TMA stores need 16-byte aligned bases and row pitch; other outputs take the register path
+    // TMA stores need 16-byte aligned bases and row pitch.  A single dense [M, N] result whose rows
+    // start on 32-byte boundaries is written straight from registers instead (256-bit stores, whole
+    // sectors): measured 1-3 % faster than staging it for TMA stores, whose shared-memory traffic
+    // slows the next tile's main loop.  Partial tiles of a split and multi-destination stores
+    // (all-gather) go through the staged path.
     bool ok = p.out != nullptr && (os.pitch * static_cast<int64_t>(sizeof(OutT))) % 16 == 0 &&
               (os.col_offset * static_cast<int64_t>(sizeof(OutT))) % 16 == 0;
     for (int d = 0; ok && d < os.n; ++d) ok = os.ptrs[d] != nullptr && reinterpret_cast<uintptr_t>(os.ptrs[d]) % 16 == 0;
+    const bool direct = os.n == 1 && p.splits == 1 && os.plain(p.N) && p.out != nullptr &&
+                        (static_cast<int64_t>(p.N) * sizeof(OutT)) % 32 == 0 && reinterpret_cast<uintptr_t>(p.out) % 32 == 0;
+    ok = ok && !direct;
     if (ok) {
       for (int d = 0; d < os.n; ++d) {
         void* base = static_cast<uint8_t*>(os.ptrs[d]) + os.col_offset * static_cast<int64_t>(sizeof(OutT));
