@@ -73,6 +73,18 @@ def _attention(q, k, v, heads):
     return o.transpose(1, 2).reshape(b, s, h)
 
 
+def _mlp(fc1, fc2):
+    """fc2(gelu(fc1(x))): quantized NVFP4 layers get the module that can fuse the middle steps into
+    fc1's epilogue once fc2 has a static input scale (``calibrate_hidden_scales``)."""
+    try:
+        from comfy_kitchen.modules import NVFP4Linear, NVFP4MLP
+        if isinstance(fc1, NVFP4Linear) and isinstance(fc2, NVFP4Linear):
+            return NVFP4MLP(fc1, fc2)
+    except ImportError:
+        pass
+    return lambda x: fc2(F.gelu(fc1(x), approximate="tanh"))
+
+
 class _Stream(nn.Module):
     def __init__(self, cfg: MMDiTConfig, device, gen, make_linear):
         super().__init__()
@@ -82,6 +94,7 @@ class _Stream(nn.Module):
         self.proj = _qlinear(h, h, device, gen, make_linear)
         self.fc1 = _qlinear(h, cfg.mlp_ratio * h, device, gen, make_linear)
         self.fc2 = _qlinear(cfg.mlp_ratio * h, h, device, gen, make_linear)
+        self.mlp = _mlp(self.fc1, self.fc2)
 
 
 class DoubleBlock(nn.Module):
@@ -105,7 +118,7 @@ class DoubleBlock(nn.Module):
             a = attn[:, start:start + x.shape[1]]
             start += x.shape[1]
             x = torch.addcmul(x, m[2].unsqueeze(1), st.proj(a))
-            x = torch.addcmul(x, m[5].unsqueeze(1), st.fc2(F.gelu(st.fc1(_modulate(x, m[3], m[4])), approximate="tanh")))
+            x = torch.addcmul(x, m[5].unsqueeze(1), st.mlp(_modulate(x, m[3], m[4])))
             outs.append(x)
         return outs[1], outs[0]
 
@@ -125,6 +138,7 @@ class SingleBlock(nn.Module):
         self.linear1_mlp = _qlinear(h, r * h, device, gen, make_linear)
         self.linear2_attn = _qlinear(h, h, device, gen, make_linear)
         self.linear2_mlp = _qlinear(r * h, h, device, gen, make_linear)
+        self.mlp = _mlp(self.linear1_mlp, self.linear2_mlp)
 
     def forward(self, x, vec):
         shift, scale, gate = self.mod(F.silu(vec)).chunk(3, dim=-1)
@@ -134,13 +148,12 @@ class SingleBlock(nn.Module):
             b, s_, _ = xin.shape
             xq = quantize(xin.reshape(b * s_, self.h))
             q, k, v = self.linear1_qkv(xq).reshape(b, s_, 3 * self.h).chunk(3, dim=-1)
-            mlp = self.linear1_mlp(xq).reshape(b, s_, -1)
+            mlp = self.mlp(xq).reshape(b, s_, -1)
         else:
             q, k, v = self.linear1_qkv(xin).chunk(3, dim=-1)
-            mlp = self.linear1_mlp(xin)
+            mlp = self.mlp(xin)
         attn = _attention(q, k, v, self.heads)
-        out = self.linear2_attn(attn) + self.linear2_mlp(F.gelu(mlp, approximate="tanh"))
-        return torch.addcmul(x, gate.unsqueeze(1), out)
+        return torch.addcmul(x, gate.unsqueeze(1), self.linear2_attn(attn) + mlp)
 
 
 class MMDiTStack(nn.Module):
@@ -158,6 +171,23 @@ class MMDiTStack(nn.Module):
         for blk in self.single_stream:
             x = blk(x, vec)
         return x[:, txt.shape[1]:]
+
+
+def calibrate_hidden_scales(model: nn.Module, img, txt, vec) -> int:
+    """One forward in which every fusable MLP records a static scale for its hidden tensor from the
+    activations it sees (amax / 2688, what the dynamic path computes per call); later forwards then
+    run those MLPs with GELU and the hidden tensor's quantization inside the first GEMM's epilogue.
+    Returns the number of MLPs switched."""
+    from comfy_kitchen.modules import NVFP4MLP
+    mlps = [m for m in model.modules() if isinstance(m, NVFP4MLP)]
+    hooks = [m.register_forward_pre_hook(lambda mod, args: (mod.calibrate(args[0]), None)[1]) for m in mlps]
+    try:
+        with torch.inference_mode():
+            model(img, txt, vec)
+    finally:
+        for h in hooks:
+            h.remove()
+    return sum(1 for m in mlps if m.fusable())
 
 
 def make_inputs(cfg: MMDiTConfig, batch: int, device, seed: int = 0):

@@ -12,6 +12,9 @@ quantized-linear path without writing that glue again:
   per call by the one-kernel amax).
 * ``MXFP8Linear`` is the MXFP8 counterpart (``weight`` float8_e4m3fn / uint8, ``weight_scale``
   E8M0 bytes).
+* ``NVFP4MLP`` runs ``fc2(gelu_tanh(fc1(x)))`` on two NVFP4 layers with the activation and the
+  quantization of the hidden tensor fused into the first GEMM's epilogue, when the second layer
+  has a static ``input_scale``.
 * ``patch_model`` swaps every suitable ``nn.Linear`` of a model in place.
 * ``quantize_state_dict`` turns the dense weights of a checkpoint into those keys (the offline
   quantizer; runs the library's kernels, so it needs the GPU).
@@ -224,6 +227,66 @@ class MXFP8Linear(_QuantizedLinearBase):
 
     def _quantize_input(self, x: torch.Tensor) -> QuantizedTensor:
         return QuantizedTensor.from_float(x, MXFP8)
+
+
+class NVFP4MLP(nn.Module):
+    """``fc2(gelu_tanh(fc1(x)))`` on two ``NVFP4Linear`` layers.
+
+    When ``fc2`` carries a static ``input_scale`` (checkpoint key of the reference's layer,
+    samples/nvfp4_linear.py:39-74), the first GEMM's epilogue applies the activation and quantizes the
+    hidden tensor against that scale: the dense hidden tensor is never written and the separate GELU,
+    tensor-scale and quantize kernels disappear.  Bit-identical to running
+    ``fc1`` -> GELU -> ``quantize_nvfp4(h, input_scale)`` -> ``fc2`` one after the other.  Without
+    the static scale the layers run unfused with a dynamic scale; ``calibrate`` derives a static
+    scale from a sample (amax / 2688, the rule the dynamic path applies per call).
+    """
+
+    def __init__(self, fc1: NVFP4Linear, fc2: NVFP4Linear) -> None:
+        super().__init__()
+        if fc1.out_features != fc2.in_features:
+            raise ValueError(f"fc1 produces {fc1.out_features} features, fc2 takes {fc2.in_features}")
+        self.fc1 = fc1
+        self.fc2 = fc2
+
+    @torch.no_grad()
+    def calibrate(self, x: torch.Tensor) -> torch.Tensor:
+        """Set ``fc2.input_scale`` from the hidden tensor this input produces; returns the scale."""
+        from .backends import cuda as backend
+        h = torch.nn.functional.gelu(self.fc1(x), approximate="tanh")
+        scale = backend.nvfp4_tensor_scale(h.reshape(-1, h.shape[-1]).contiguous()).reshape(())
+        self.fc2.input_scale = nn.Parameter(scale.to(torch.float32), requires_grad=False)
+        return scale
+
+    def fusable(self) -> bool:
+        return self.fc2.input_scale is not None and self.fc1.out_features % 64 == 0 and \
+            self.fc1.compute_dtype in (torch.bfloat16, torch.float16)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.fusable():
+            return self.fc2(torch.nn.functional.gelu(self.fc1(x), approximate="tanh"))
+        from .backends import cuda as backend
+        shape = None
+        if isinstance(x, QuantizedTensor):
+            xq = x
+        else:
+            shape = x.shape
+            if x.dim() != 2:
+                x = x.reshape(-1, shape[-1])
+            xq = self.fc1.quantize_input(x)
+        rows = xq._params.orig_shape[0]
+        w1, w2 = self.fc1.weight, self.fc2.weight
+        dtype = self.fc1.compute_dtype
+        _, codes, block_scales = backend.linear_nvfp4_fused(
+            xq._qdata, w1._qdata, xq._params.scale, w1._params.scale, xq._params.block_scale, w1._params.block_scale,
+            bias=self.fc1.bias, activation="gelu_tanh", out_dtype=dtype, requant_scale=self.fc2.input_scale,
+            return_dense=False)
+        y = backend.scaled_mm_nvfp4(codes, w2._qdata, self.fc2.input_scale, w2._params.scale, block_scales,
+                                    w2._params.block_scale, bias=self.fc2.bias, out_dtype=dtype)
+        if y.shape[0] != rows:
+            y = y[:rows]
+        if shape is not None and len(shape) != 2:
+            y = y.reshape(*shape[:-1], self.fc2.out_features)
+        return y
 
 
 _LAYERS = {"nvfp4": NVFP4Linear, "mxfp8": MXFP8Linear, NVFP4: NVFP4Linear, MXFP8: MXFP8Linear}

@@ -241,3 +241,26 @@ def test_captured_graph_survives_growth_of_the_cached_scratch_buffers(ck, cuda_d
             graph.replay()
             side.synchronize()
             assert torch.equal(y, eager)
+
+
+@pytest.mark.parametrize("rows", [200, 77])  # 77: rows padded to 16 inside the quantizer
+def test_nvfp4_mlp_fused_equals_the_unfused_layers(ck, cuda_device, rows):
+    """fc1 -> GELU -> quantize (static scale) -> fc2 with the middle steps in fc1's epilogue: same bits."""
+    from comfy_kitchen.modules import NVFP4Linear, NVFP4MLP
+
+    fc1 = NVFP4Linear.from_linear(_dense(cuda_device, 256, 512, seed=1))
+    fc2 = NVFP4Linear.from_linear(_dense(cuda_device, 512, 256, seed=2))
+    mlp = NVFP4MLP(fc1, fc2)
+    x = torch.randn(2, rows // 2 if rows % 2 == 0 else rows, 256, device=cuda_device, dtype=torch.bfloat16)
+    x = x[:1] if rows % 2 else x  # [1, 77, 256] or [2, 100, 256]
+    with torch.inference_mode():
+        assert not mlp.fusable()
+        dynamic = mlp(x)  # no static scale yet: plain layers, dynamic hidden scale
+        assert torch.equal(dynamic, fc2(torch.nn.functional.gelu(fc1(x), approximate="tanh")))
+        scale = mlp.calibrate(x)
+        assert mlp.fusable() and float(scale) > 0
+        fused = mlp(x)
+        unfused = fc2(torch.nn.functional.gelu(fc1(x), approximate="tanh"))  # fc2 now quantizes against the static scale
+    assert fused.shape == unfused.shape == (*x.shape[:-1], 256)
+    assert torch.equal(fused, unfused)
+    assert "fc2.input_scale" in mlp.state_dict()
