@@ -53,6 +53,16 @@ constexpr int kMmaPerStage = kStageKBytes / kMmaKBytes;
 // Epilogue warps per CTA: two per 32-lane quarter of tensor memory for the plain epilogue,
 // four for the fused one (its activation + quantization arithmetic is ~30 instructions per
 // element and must keep up with the tensor pipe), one for a 64-wide tile.
+// Timeline builds (-DCK_GEMM_TRACE) keep per-tile stamps in shared memory behind the barriers.
+#ifdef CK_GEMM_TRACE
+constexpr int kTraceTiles = 40;
+constexpr int kTraceSlots = 16;
+constexpr int kTraceSmemTiles = 12;
+constexpr int kTraceSmemBytes = kTraceSmemTiles * kTraceSlots * 4;
+#else
+constexpr int kTraceSmemBytes = 0;
+#endif
+
 constexpr int epilogue_warps(bool fused, int tile_n) { return (fused && tile_n >= 256) ? 16 : (tile_n <= 64) ? 4 : 8; }
 constexpr int num_threads(bool fused, int tile_n) {
   return 64 + 32 * epilogue_warps(fused, tile_n);  // + TMA and MMA warps
@@ -86,7 +96,7 @@ struct Config {
   static constexpr int kOutStageBytes = OUT_STAGE * epilogue_warps(false, TILE_N) * 4096;
   static constexpr int kRingBytes = (STAGES * kStageBytes + 1023) / 1024 * 1024;
   static constexpr int kSmemBytes = kRingBytes + kOutStageBytes + 3 * TILE_N * 4 /*bias*/ +
-                                    1024 /*alignment slack*/ + 256 /*barriers*/;
+                                    1024 /*alignment slack*/ + 256 /*barriers*/ + kTraceSmemBytes;
   // tensor memory columns
   static constexpr int kAccCols = TILE_N;
   static constexpr int kSfaCol = NUM_ACC * kAccCols;
@@ -149,9 +159,12 @@ struct OutputMaps {
 };
 
 // Optional per-tile timeline (SM cycle counter) for tuning; compiled in with -DCK_GEMM_TRACE only.
+// Per-tile stamps are kept in shared memory (32-bit counts, 12 tiles x 16 slots) and written out
+// when the CTA is done: a stamp costs one shared-memory store, so the instrumented kernel behaves
+// like the production one (global stores in the loops would queue behind the epilogue's).
+// -DCK_GEMM_TRACE_STAGES adds per-stage stamps of the MMA warp, stored to global memory as they
+// are taken (these do perturb the kernel).
 #ifdef CK_GEMM_TRACE
-constexpr int kTraceTiles = 40;
-constexpr int kTraceSlots = 16;
 __device__ long long g_trace[160 * kTraceTiles * kTraceSlots];
 __device__ long long g_trace2[160 * 4 * 64];
 // per launch (ring of 8) and CTA: global timer (ns) and SM clock at entry, after the dependency wait, at exit
@@ -169,19 +182,23 @@ __device__ __forceinline__ long long global_timer_ns() {
       t3[1] = clock64();                                                                             \
     }                                                                                                \
   } while (0)
+#ifdef CK_GEMM_TRACE_STAGES
 #define CK_TRACE2(kind, idx)                                                                         \
   do {                                                                                               \
     if (lane == 0 && (idx) < 64 && blockIdx.x < 160) g_trace2[(blockIdx.x * 4 + (kind)) * 64 + (idx)] = clock64(); \
   } while (0)
+#else
+#define CK_TRACE2(kind, idx) \
+  do {                       \
+  } while (0)
+#endif
 #define CK_TRACE(slot)                                                                               \
   do {                                                                                               \
-    if (lane == 0 && tile_it < kTraceTiles && blockIdx.x < 160)                                      \
-      g_trace[(blockIdx.x * kTraceTiles + tile_it) * kTraceSlots + (slot)] = clock64();             \
+    if (lane == 0 && tile_it < kTraceSmemTiles) trace_s[tile_it * kTraceSlots + (slot)] = static_cast<uint32_t>(clock64()); \
   } while (0)
 #define CK_TRACE_ELECTED(slot)                                                                       \
   do {                                                                                               \
-    if (tile_it < kTraceTiles && blockIdx.x < 160)                                                   \
-      g_trace[(blockIdx.x * kTraceTiles + tile_it) * kTraceSlots + (slot)] = clock64();             \
+    if (tile_it < kTraceSmemTiles) trace_s[tile_it * kTraceSlots + (slot)] = static_cast<uint32_t>(clock64()); \
   } while (0)
 #else
 #define CK_TRACE3(slot) \
@@ -231,7 +248,7 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[32],
             o.w[j] = *reinterpret_cast<uint32_t*>(&q);
           }
         }
-        st_global_256(reinterpret_cast<uint8_t*>(dst) + h * 32, o);
+        st_global_256_no_allocate(reinterpret_cast<uint8_t*>(dst) + h * 32, o);
       }
     } else {
 #pragma unroll
@@ -239,7 +256,7 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[32],
         Vec256 o;
 #pragma unroll
         for (int j = 0; j < 8; ++j) o.w[j] = __float_as_uint(v[h * 8 + j]);
-        st_global_256(reinterpret_cast<uint8_t*>(dst) + h * 32, o);
+        st_global_256_no_allocate(reinterpret_cast<uint8_t*>(dst) + h * 32, o);
       }
     }
     return;
@@ -357,6 +374,9 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint64_t* acc_empty_bar = acc_full_bar + NUM_ACC;  // [NUM_ACC] epilogue -> MMA
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + NUM_ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+#ifdef CK_GEMM_TRACE
+  uint32_t* trace_s = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + 256);
+#endif
   static_assert((2 * STAGES + 2 * NUM_ACC) * 8 + 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5;
@@ -370,6 +390,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   // needs the other CTA's barriers to exist.
   uint32_t tmem_base = 0;
   if (warp == 0) {
+#ifdef CK_GEMM_TRACE
+    for (int i = lane; i < kTraceSmemTiles * kTraceSlots; i += 32) trace_s[i] = 0u;
+    __syncwarp();
+#endif
     if (lane == 0) {
       *abort_flag = 0;
       for (int s = 0; s < STAGES; ++s) {
@@ -910,8 +934,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     o0.w[i] = pk[c][i];
                     o1.w[i] = pk[c][8 + i];
                   }
-                  st_global_256(out_row + c * 32, o0);
-                  st_global_256(out_row + c * 32 + 16, o1);
+                  st_global_256_no_allocate(out_row + c * 32, o0);
+                  st_global_256_no_allocate(out_row + c * 32 + 16, o1);
                 } else {
 #pragma unroll
                   for (int i = 0; i < 16; ++i) {  // N % 8 == 0: pairs never straddle the edge
@@ -1004,6 +1028,13 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   tc_fence_before_sync();
   __syncthreads();
   CK_TRACE3(3);
+#ifdef CK_GEMM_TRACE
+  if (blockIdx.x < 160) {
+    for (int i = threadIdx.x; i < kTraceSmemTiles * kTraceSlots; i += blockDim.x) {
+      g_trace[(blockIdx.x * kTraceTiles + i / kTraceSlots) * kTraceSlots + i % kTraceSlots] = trace_s[i];
+    }
+  }
+#endif
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(p.status, 1);
     // give copies that may still be in flight time to land before the CTA's memory is released

@@ -1,19 +1,21 @@
 """Per-role timeline of the block-scaled GEMM kernel (tuning aid).
 
-    python comfy-kitchen_b200/gemm_timeline.py build            # cross-compiles; no GPU needed
+    python comfy-kitchen_b200/gemm_timeline.py build [--stages]   # cross-compiles; no GPU needed
     python comfy-kitchen_b200/gemm_timeline.py run [M,N,K] [--ring 8] [--verbose]
 
 ``build`` compiles csrc/*.cu with -DCK_GEMM_TRACE into lib/libck_b200_trace.so: the same
-kernels, with the SM cycle counter (and the global nanosecond timer at CTA entry, after set-up,
-after the dependency wait and at the end) written to a device buffer at fixed points of each
-role's loop.  ``run`` replays a CUDA graph of 16 back-to-back NVFP4 GEMM launches over a ring of
+kernels, with the SM cycle counter recorded at fixed points of each role's per-tile loop (kept in
+shared memory, written out when the CTA is done: the kernel then runs within ~1 % of the
+production build) and the global nanosecond timer at CTA entry, after set-up, after the
+dependency wait and at the end.  ``--stages`` adds per-stage stamps of the MMA warp, stored to
+global memory as they are taken (they slow the kernel by several per cent and stall behind the
+epilogue's stores; printed by ``run --verbose``).  ``run`` replays a CUDA graph of 16 back-to-back NVFP4 GEMM launches over a ring of
 operand sets (so that operands come from DRAM, as in the benchmark), reads the buffers back and
 prints, for the last launches: when CTAs entered / passed the dependency wait / finished, the
 SM clock the counters imply, and for a few CTAs the cycle at which each tile's first and last
 stage landed, its accumulator was handed over, drained and stored.  The figures quoted in
-profiles/scaled_mm_nvfp4_pair_*.md come from this tool.  The instrumented library is slower
-than the production one by a few per cent; it is never loaded by the package unless CK_LIB
-points at it.
+profiles/scaled_mm_nvfp4_pair_*.md come from this tool.  The instrumented library is never
+loaded by the package unless CK_LIB points at it.
 """
 from __future__ import annotations
 
@@ -29,7 +31,7 @@ TRACE_LIB = os.path.join(HERE, "lib", "libck_b200_trace.so")
 OBJ_DIR = os.path.join(HERE, "build", "trace")
 
 
-def build() -> str:
+def build(stages: bool = False) -> str:
     sys.path.insert(0, HERE)
     import build as base  # the production build recipe: same flags plus the trace macro
 
@@ -40,7 +42,8 @@ def build() -> str:
     for src in base._sources():
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        procs.append(subprocess.Popen([nvcc, *base.NVCC_FLAGS, "-DCK_GEMM_TRACE", "-c", src, "-o", obj],
+        macros = ["-DCK_GEMM_TRACE"] + (["-DCK_GEMM_TRACE_STAGES"] if stages else [])
+        procs.append(subprocess.Popen([nvcc, *base.NVCC_FLAGS, *macros, "-c", src, "-o", obj],
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     for p in procs:
         out, _ = p.communicate()
@@ -97,7 +100,7 @@ def run(shape: str, ring: int, verbose: bool) -> None:
         with torch.cuda.graph(g, stream=side):
             for i in range(launches):
                 launch(i, side.cuda_stream)
-        for _ in range(3):
+        for _ in range(60):  # ~20 ms: lets the SM clock ramp up before the replay that is kept
             g.replay()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -147,15 +150,18 @@ def run(shape: str, ring: int, verbose: bool) -> None:
         base = b[last, cta, 0, 1]
         print(f"--- CTA {cta}: cycles since its entry; set-up done {b[last, cta, 1, 1] - base}, dependency wait done "
               f"{b[last, cta, 2, 1] - base}, body done {b[last, cta, 3, 1] - base}")
-        for t in range(6):
+        for t in range(12):  # the kernel keeps the stamps of its first 12 tiles (low 32 bits of the counter)
             row = tiles[cta, t]
             if not row.any():
                 break
-            print(f"  tile {t}: " + "  ".join(f"{nm}={int(v - base)}" for nm, v in zip(slots, row) if v))
+            print(f"  tile {t}: " + "  ".join(f"{nm}={(int(v) - int(base)) & 0xFFFFFFFF}" for nm, v in zip(slots, row) if v))
     if verbose and not small:
         per_stage = np.zeros((160, 4, 64), dtype=np.int64)
         lib.ck_debug_trace2.argtypes = [ctypes.c_void_p]
         assert lib.ck_debug_trace2(per_stage.ctypes.data) == 0
+        if not per_stage.any():
+            print("(no per-stage stamps: build with --stages)")
+            return
         nst = min(48, 3 * ((k // 2 + 127) // 128))
         w_ = per_stage[0, 2, :nst] - per_stage[0, 1, :nst]
         iss = per_stage[0, 3, :nst] - per_stage[0, 2, :nst]
@@ -172,8 +178,9 @@ if __name__ == "__main__":
     ap.add_argument("shape", nargs="?", default="4096,3072,3072")
     ap.add_argument("--ring", type=int, default=8)
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--stages", action="store_true", help="build: also record per-stage stamps of the MMA warp")
     a = ap.parse_args()
     if a.command == "build":
-        print(build())
+        print(build(a.stages))
     else:
         run(a.shape, a.ring, a.verbose)
