@@ -1036,11 +1036,18 @@ def run_gpu_arm(args) -> dict | None:
         # per-kernel timings for the rooflines and the one-call path (same buffers, each alone)
         extra = {}
         if full:
+            # The one-call path, timed exactly like the headline step (same replay time, same ring).
+            l2, _, fl2, by2 = make_steps(lib, wl, "linear_onecall")
+            t2 = time_replays(torch, l2, args.steps, args.warmup, use_graph, dist)
+            extra["linear_onecall"] = (t2["median_ms"] / args.steps, fl2, by2, t2["best_ms"] / args.steps)
             # Each kernel alone: the median of 11 replays of the K-launch graph (a few ms in all - the
-            # kernel "timed alone", to be read against the burst peak) and, for the GEMM, also the median
-            # over ~0.2 s of back-to-back replays (the GPU settles under its power cap: sustained peak).
-            for name in ("gemm_nvfp4", "quantize_nvfp4", "gemm_mxfp8", "quantize_mxfp8", "linear_onecall", "copy_floor"):
+            # kernel "timed alone", to be read against the burst peak; the GPU idles for 0.75 s before each
+            # pass so that the load of the pass before has left its power average) and, for the GEMM, also
+            # the median over ~0.2 s of back-to-back replays (the GPU settles under its power cap: sustained peak).
+            for name in ("gemm_nvfp4", "quantize_nvfp4", "gemm_mxfp8", "quantize_mxfp8", "copy_floor"):
                 l2, _, fl2, by2 = make_steps(lib, wl, name)
+                torch.cuda.synchronize()
+                time.sleep(0.75)
                 t2 = time_replays(torch, l2, args.steps, args.warmup, use_graph, dist, min_seconds=0.0, min_replays=11)
                 extra[name] = (t2["median_ms"] / args.steps, fl2, by2, t2["best_ms"] / args.steps)
             l2 = make_steps(lib, wl, "gemm_nvfp4")[0]
@@ -1148,7 +1155,7 @@ def run_gpu_arm(args) -> dict | None:
 
     if full:
         line["roofline"] = tensor_roofline(extra["gemm_nvfp4"][0], extra["gemm_nvfp4"][1], fp4_peak, NOMINAL_FP4_TFLOPS, "scaled_mm_nvfp4")
-        line["roofline"]["timing"] = "median of 11 replays of a graph of K launches (kernel alone, a few ms): read against the burst peak"
+        line["roofline"]["timing"] = "median of 11 replays of a graph of K launches after 0.75 s of idling (kernel alone, a few ms): read against the burst peak"
         line["roofline"]["best_us_per_launch"] = extra["gemm_nvfp4"][3] * 1e3
         sus_peak = 4.0 * peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
         sus = extra["gemm_nvfp4"][1] / (sustained_gemm_ms * 1e-3) / 1e12
