@@ -133,6 +133,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Asks L2 for the box a later tiled load will fetch (no destination, nothing to wait for).  The
+// same alignment rule as for the load: x * element size a multiple of 16 bytes.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+
 // CTA-pair forms: the data lands in the executing CTA's shared memory, the byte count is
 // reported to the barrier at the same offset in the pair's leader (even-ranked) CTA.  In the
 // cluster-wide shared address space bit 24 of an address selects the CTA of the pair.
