@@ -752,6 +752,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int b_row = n0 + c0 + c * 32 + i;  // activation row = output row
+              if (c == 0 && i == 1 && warp == 2) CK_TRACE(14);
+              if (c == 0 && i == 8 && warp == 2) CK_TRACE(15);
               if (b_row < p.N) {
                 const float y = fmaf(__uint_as_float(buf[c][i]), alpha, bias_v);
                 if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
