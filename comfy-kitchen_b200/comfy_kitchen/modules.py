@@ -29,7 +29,7 @@ import torch
 import torch.nn as nn
 
 from .tensor import QuantizedTensor, TensorCoreMXFP8Layout, TensorCoreNVFP4Layout
-from .tensor.blockwise import quantized_linear
+from .tensor.blockwise import direct_backend, quantized_linear, strict_mode, strict_status_check
 
 NVFP4 = "TensorCoreNVFP4Layout"
 MXFP8 = "TensorCoreMXFP8Layout"
@@ -183,6 +183,31 @@ class NVFP4Linear(_QuantizedLinearBase):
 
     def _quantize_input(self, x: torch.Tensor) -> QuantizedTensor:
         return QuantizedTensor.from_float(x, NVFP4, scale=self.input_scale)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Dense CUDA activations take the one-call path (tensor scale, quantize and GEMM enqueued by a
+        single library call: a third of the host time per layer of the layout path, same bits); quantized
+        inputs, traced calls and anything the call refuses take the layout path."""
+        w = self.weight
+        if not isinstance(x, QuantizedTensor) and w is not None and x.dim() >= 2 and x.shape[-1] % 32 == 0 and \
+                x.dtype in (torch.bfloat16, torch.float16, torch.float32) and not getattr(w._params, "transposed", False):
+            backend = direct_backend(x, w._qdata, self.bias, self.input_scale)
+            if backend is not None:
+                shape = x.shape
+                x2 = x.reshape(-1, shape[-1])
+                if not x2.is_contiguous():
+                    x2 = x2.contiguous()
+                try:
+                    y = backend.linear_nvfp4_from_float(x2, w._qdata, w._params.scale, w._params.block_scale, bias=self.bias,
+                                                        x_scale=self.input_scale, out_dtype=x.dtype)
+                    strict_status_check("NVFP4Linear")
+                    if y.shape[1] != self.out_features:  # weight rows padded to the block size
+                        y = y[:, :self.out_features]
+                    return y if len(shape) == 2 else y.reshape(*shape[:-1], self.out_features)
+                except (RuntimeError, TypeError, AssertionError):
+                    if strict_mode():
+                        raise
+        return super().forward(x)
 
 
 class MXFP8Linear(_QuantizedLinearBase):
