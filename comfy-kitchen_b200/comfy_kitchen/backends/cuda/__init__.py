@@ -26,6 +26,7 @@ __all__ = [
     "scaled_mm_mxfp8",
     "linear_nvfp4_fused",
     "linear_nvfp4_from_float",
+    "linear_mxfp8_from_float",
     "nvfp4_tensor_scale",
     "check_device_status",
 ]
@@ -62,6 +63,8 @@ _SIGNATURES = {
     "ck_linear_nvfp4_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _P],
     "ck_linear_nvfp4_from_float_workspace_bytes": [_L, _L, _I],
     "ck_linear_nvfp4_from_float": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
+    "ck_linear_mxfp8_from_float_workspace_bytes": [_L, _L],
+    "ck_linear_mxfp8_from_float": [_P, _I, _P, _P, _P, _I, _P, _I, _L, _L, _L, _P, _L, _P],
     "ck_scaled_mm_nvfp4_allgather": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "ck_scaled_mm_mxfp8_allgather": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "ck_peer_barrier": [_P, _I, _I, ctypes.c_uint32, _P],
@@ -71,7 +74,8 @@ _SIGNATURES = {
     "ck_dequantize_mxfp8": [_P, _P, _P, _I, _L, _L, _P],
 }
 _RESTYPE = {"ck_last_error": ctypes.c_char_p, "ck_nvfp4_tensor_scale_scratch_bytes": ctypes.c_int64,
-            "ck_scaled_mm_workspace_bytes": ctypes.c_int64, "ck_linear_nvfp4_from_float_workspace_bytes": ctypes.c_int64}
+            "ck_scaled_mm_workspace_bytes": ctypes.c_int64, "ck_linear_nvfp4_from_float_workspace_bytes": ctypes.c_int64,
+            "ck_linear_mxfp8_from_float_workspace_bytes": ctypes.c_int64}
 
 
 def library_path() -> str:
@@ -461,6 +465,41 @@ def linear_nvfp4_from_float(x: torch.Tensor, w_codes: torch.Tensor, w_scale: tor
         _check(lib.ck_linear_nvfp4_from_float(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(sx), _ptr(w_codes), _ptr(w_block_scales),
                                               _ptr(sw), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
                                               ws.data_ptr(), ws.numel(), _stream(dev)), "linear_nvfp4_from_float")
+    del bias_keep
+    return out
+
+
+def linear_mxfp8_from_float(x: torch.Tensor, w_data: torch.Tensor, w_block_scales: torch.Tensor,
+                            bias: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """MXFP8 linear on a dense activation in one library call: quantize -> GEMM.  ``x`` [M, K] float;
+    ``w_data`` float8_e4m3fn [N, K] with its tiled E8M0 ``w_block_scales``.  Same bits as
+    ``quantize_mxfp8`` followed by ``scaled_mm_mxfp8``; the quantized activation goes to a workspace
+    cached per device and stream."""
+    lib = load_library()
+    x, w_data, w_block_scales = _plain(x), _plain(w_data), _plain(w_block_scales)
+    assert x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2-D tensor"
+    m, k = x.shape
+    n, kb = w_data.shape
+    assert kb == k, "Matrix dimensions do not match"
+    assert k % 32 == 0 and n % 8 == 0, "K must be a multiple of 32 and N of 8"
+    assert tuple(w_block_scales.shape) == (roundup(n, 128), roundup(k // 32, 4)), "Invalid B scale shape"
+    assert w_data.is_contiguous() and w_block_scales.is_contiguous()
+    dev = x.device
+    out_dtype = out_dtype or (x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16)
+    bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
+    need = int(lib.ck_linear_mxfp8_from_float_workspace_bytes(m, k))
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream, "mxfp8")  # not shared with the NVFP4 path (its zeroed head)
+    ws = _linear_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        _linear_workspaces[key] = ws
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib.ck_linear_mxfp8_from_float(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(w_data), _ptr(w_block_scales), bias_ptr,
+                                              bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, ws.data_ptr(),
+                                              ws.numel(), _stream(dev)), "linear_mxfp8_from_float")
     del bias_keep
     return out
 

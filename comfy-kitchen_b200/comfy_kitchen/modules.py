@@ -253,6 +253,29 @@ class MXFP8Linear(_QuantizedLinearBase):
     def _quantize_input(self, x: torch.Tensor) -> QuantizedTensor:
         return QuantizedTensor.from_float(x, MXFP8)
 
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Dense CUDA activations take the one-call path (quantize and GEMM enqueued by a single library
+        call, same bits); everything else the layout path."""
+        w = self.weight
+        if not isinstance(x, QuantizedTensor) and w is not None and x.dim() >= 2 and x.shape[-1] % 32 == 0 and \
+                x.dtype in (torch.bfloat16, torch.float16, torch.float32) and not getattr(w._params, "transposed", False):
+            backend = direct_backend(x, w._qdata, self.bias)
+            if backend is not None:
+                shape = x.shape
+                x2 = x.reshape(-1, shape[-1])
+                if not x2.is_contiguous():
+                    x2 = x2.contiguous()
+                try:
+                    y = backend.linear_mxfp8_from_float(x2, w._qdata, w._params.scale, bias=self.bias, out_dtype=x.dtype)
+                    strict_status_check("MXFP8Linear")
+                    if y.shape[1] != self.out_features:  # weight rows padded to the block size
+                        y = y[:, :self.out_features]
+                    return y if len(shape) == 2 else y.reshape(*shape[:-1], self.out_features)
+                except (RuntimeError, TypeError, AssertionError):
+                    if strict_mode():
+                        raise
+        return super().forward(x)
+
 
 class NVFP4MLP(nn.Module):
     """``fc2(gelu_tanh(fc1(x)))`` on two ``NVFP4Linear`` layers.

@@ -67,3 +67,28 @@ extern "C" int ck_linear_nvfp4_from_float(const void* x, int x_dtype, const floa
   return ck_scaled_mm_nvfp4(codes, w_codes, scales, w_block_scales, scale, w_scale, nullptr, bias, bias_dtype, out,
                             out_dtype, M, N, K, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// MXFP8: quantize -> GEMM.  Workspace layout: data [M, K] | tiled E8M0 block scales.
+// ---------------------------------------------------------------------------------------------
+extern "C" int64_t ck_linear_mxfp8_from_float_workspace_bytes(int64_t M, int64_t K) {
+  if (M <= 0 || K <= 0 || K % 32 != 0 || M >= (1ll << 30) || K >= (1ll << 30)) return 0;
+  return ck::round_up(M * K, 256) + ck::round_up(ck::round_up(M, 128) * ck::round_up(K / 32, 4), 256);
+}
+
+extern "C" int ck_linear_mxfp8_from_float(const void* x, int x_dtype, const void* w_data, const void* w_block_scales,
+                                          const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                                          int64_t K, void* workspace, int64_t workspace_bytes, void* stream) {
+  using namespace ck;
+  CK_REQUIRE(x && w_data && w_block_scales && out && workspace, "linear_mxfp8_from_float: null pointer");
+  CK_REQUIRE(M > 0 && N > 0 && K > 0 && M < (1ll << 30) && K < (1ll << 30), "linear_mxfp8_from_float: bad shape");
+  CK_REQUIRE(K % 32 == 0, "linear_mxfp8_from_float: K=%lld must be a multiple of 32", (long long)K);
+  CK_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "linear_mxfp8_from_float: workspace must be 256-byte aligned");
+  const int64_t need = ck_linear_mxfp8_from_float_workspace_bytes(M, K);
+  CK_REQUIRE(workspace_bytes >= need, "linear_mxfp8_from_float: workspace of %lld bytes, %lld needed",
+             (long long)workspace_bytes, (long long)need);
+  uint8_t* data = static_cast<uint8_t*>(workspace);
+  uint8_t* scales = data + round_up(M * K, 256);
+  if (int rc = ck_quantize_mxfp8(x, x_dtype, data, scales, M, K, M, K, stream)) return rc;
+  return ck_scaled_mm_mxfp8(data, w_data, scales, w_block_scales, bias, bias_dtype, out, out_dtype, M, N, K, stream);
+}

@@ -222,6 +222,23 @@ CK_API int ck_linear_nvfp4_from_float(const void* x, int x_dtype, const float* x
                                void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * The MXFP8 counterpart: x [M,K] is quantized to MXFP8 (E4M3 data + tiled E8M0 block scales, as
+ * ck_quantize_mxfp8 writes them) into `workspace` and multiplied with a pre-quantized weight,
+ *   out[M,N] = cast( deq(quantize(x)) . deq(w)^T + bias ),
+ * by two kernels enqueued back to back; bit-identical to ck_quantize_mxfp8 followed by
+ * ck_scaled_mm_mxfp8.  K % 32 == 0, N % 8 == 0; workspace 256-byte aligned, at least
+ * ck_linear_mxfp8_from_float_workspace_bytes(M, K) bytes (0 = shape not supported), no
+ * zero-fill needed.  Replaces QuantizedTensor.from_float -> F.linear of the reference's MXFP8
+ * layout (comfy_kitchen/tensor/mxfp8.py:45-66 followed by tensor/mxfp8.py:211-236; caller side
+ * samples/mxfp8_model_patcher.py:57-75).
+ */
+CK_API int64_t ck_linear_mxfp8_from_float_workspace_bytes(int64_t M, int64_t K);
+CK_API int ck_linear_mxfp8_from_float(const void* x, int x_dtype, const void* w_data,
+                               const void* w_block_scales, const void* bias, int bias_dtype,
+                               void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * MXFP8 GEMM with linear semantics: out[M,N] = cast(deq(a) . deq(b)^T + bias).
  * a: E4M3 bytes [M,K], b: E4M3 bytes [N,K], sfa/sfb: E8M0 block scales in the
  * swizzled layout with roundup(M|N,128) x roundup(K/32,4) bytes.  K must be a

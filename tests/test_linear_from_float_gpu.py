@@ -75,3 +75,25 @@ def test_rejects_bad_arguments(env, cuda_device):
     rc = lib.ck_linear_nvfp4_from_float(x.data_ptr(), 2, None, x.data_ptr(), x.data_ptr(), x.data_ptr(), None, 0,
                                         x.data_ptr(), 2, 128, 128, 256, small.data_ptr(), small.numel(), None)
     assert rc != 0 and b"workspace" in lib.ck_last_error()
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (48, 136, 192), (300, 520, 544), (4096, 3072, 3072)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_mxfp8_one_call_equals_separate_calls(env, cuda_device, shape, dtype):
+    ck, backend = env
+    m, n, k = shape
+    g = torch.Generator(device="cpu").manual_seed(m + n + k + 1)
+    x = torch.randn(m, k, generator=g).to(dtype).to(cuda_device)
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(cuda_device)
+    bias = (torch.randn(n, generator=g) * 0.01).bfloat16().to(cuda_device)
+    qw, bsw = ck.quantize_mxfp8(w)
+    for _ in range(2):
+        y = backend.linear_mxfp8_from_float(x, qw, bsw, bias=bias, out_dtype=torch.bfloat16)
+        qx, bsx = ck.quantize_mxfp8(x)
+        ref = ck.scaled_mm_mxfp8(qx, qw, bsx, bsw, bias=bias, out_dtype=torch.bfloat16)
+        assert torch.equal(y, ref)
+    backend.check_device_status("linear_mxfp8_from_float")
+    lib = backend.load_library()
+    assert lib.ck_linear_mxfp8_from_float_workspace_bytes(128, 48) == 0  # K not a multiple of 32
+    assert lib.ck_linear_mxfp8_from_float(x.data_ptr(), 2, qw.data_ptr(), bsw.data_ptr(), None, 2, y.data_ptr(), 2, m, n, k,
+                                          None, 0, None) != 0  # no workspace
