@@ -127,6 +127,28 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on_device(device):
+    """Context that makes ``device`` current for the library call; no device switch (several
+    microseconds of host time per call) when it already is."""
+    if not isinstance(device, torch.device):
+        device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+    index = device.index
+    if index is None or index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _plain(t):
     return t.data if isinstance(t, torch.nn.Parameter) else t
 
@@ -163,7 +185,7 @@ def quantize_nvfp4(x: torch.Tensor, per_tensor_scale: torch.Tensor, epsilon: flo
     scale = _scalar_f32(per_tensor_scale, x.device, "per_tensor_scale")
     qx = torch.empty((out_rows, out_cols // 2), device=x.device, dtype=torch.uint8)
     sx = torch.empty((roundup(out_rows, 128), roundup(out_cols // 16, 4)), device=x.device, dtype=torch.uint8)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.ck_quantize_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(scale), _ptr(qx), _ptr(sx), rows, cols,
                                      out_rows, out_cols, int(bool(hi_first)), _stream(x.device)), "quantize_nvfp4")
     return qx, sx.view(torch.float8_e4m3fn)
@@ -182,7 +204,7 @@ def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor
         assert out_cols % 32 == 0, f"num_cols must be divisible by 32, got {out_cols}"
     qx = torch.empty((out_rows, out_cols), device=x.device, dtype=torch.uint8)
     sx = torch.empty((roundup(out_rows, 128), roundup(out_cols // 32, 4)), device=x.device, dtype=torch.uint8)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.ck_quantize_mxfp8(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(qx), _ptr(sx), rows, cols, out_rows,
                                      out_cols, _stream(x.device)), "quantize_mxfp8")
     return qx.view(torch.float8_e4m3fn), sx.view(torch.float8_e8m0fnu)
@@ -219,7 +241,7 @@ def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
     stream = _stream(x.device)
     scratch = _scale_scratch_for(x.device, stream, lib.ck_nvfp4_tensor_scale_scratch_bytes(n))
     out = torch.empty((), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.ck_nvfp4_tensor_scale(_ptr(x), DTYPE_TO_CODE[x.dtype], n, _ptr(out), _ptr(scratch), scratch.numel(),
                                          stream), "nvfp4_tensor_scale")
     return out
@@ -237,7 +259,7 @@ def dequantize_nvfp4(qx: torch.Tensor, per_tensor_scale: torch.Tensor, block_sca
     assert tuple(block_scales.shape) == (roundup(rows, 128), roundup(cols // 16, 4)), "Invalid scale shape"
     scale = _scalar_f32(per_tensor_scale, qx.device, "per_tensor_scale")
     out = torch.empty((rows, cols), device=qx.device, dtype=output_type)
-    with torch.cuda.device(qx.device):
+    with _on_device(qx.device):
         _check(lib.ck_dequantize_nvfp4(_ptr(qx), _ptr(scale), _ptr(block_scales), _ptr(out), DTYPE_TO_CODE[output_type],
                                        rows, cols, int(bool(hi_first)), _stream(qx.device)), "dequantize_nvfp4")
     return out
@@ -253,7 +275,7 @@ def dequantize_mxfp8(qx: torch.Tensor, block_scales: torch.Tensor,
     assert cols % 32 == 0, f"num_cols must be divisible by 32, got {cols}"
     assert tuple(block_scales.shape) == (roundup(rows, 128), roundup(cols // 32, 4)), "Invalid scale shape"
     out = torch.empty((rows, cols), device=qx.device, dtype=output_type)
-    with torch.cuda.device(qx.device):
+    with _on_device(qx.device):
         _check(lib.ck_dequantize_mxfp8(_ptr(qx), _ptr(block_scales), _ptr(out), DTYPE_TO_CODE[output_type], rows, cols,
                                        _stream(qx.device)), "dequantize_mxfp8")
     return out
@@ -302,7 +324,7 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
     alpha_t = None if alpha is None else _scalar_f32(alpha, dev, "alpha")
     bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         ws_ptr, ws_bytes = _gemm_workspace(lib, False, m, n, k, dev)
         _check(lib.ck_scaled_mm_nvfp4_ws(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa), _ptr(tsb),
                                          _ptr(alpha_t), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
@@ -361,7 +383,7 @@ def scaled_mm_nvfp4_allgather(a, b, tensor_scale_a, tensor_scale_b, block_scale_
     alpha_t = None if alpha is None else _scalar_f32(alpha, dev, "alpha")
     bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
     arr = _pointer_array(out_ptrs)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _check(lib.ck_scaled_mm_nvfp4_allgather(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa),
                                                 _ptr(tsb), _ptr(alpha_t), bias_ptr, bias_code, arr, len(out_ptrs),
                                                 DTYPE_TO_CODE[out_dtype], m, n, k, n_total, col_offset, _stream(dev)),
@@ -382,7 +404,7 @@ def scaled_mm_mxfp8_allgather(a, b, block_scale_a, block_scale_b, out_ptrs, n_to
     dev = a.device
     bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
     arr = _pointer_array(out_ptrs)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _check(lib.ck_scaled_mm_mxfp8_allgather(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), bias_ptr,
                                                 bias_code, arr, len(out_ptrs), DTYPE_TO_CODE[out_dtype], m, n, k, n_total,
                                                 col_offset, _stream(dev)), "scaled_mm_mxfp8_allgather")
@@ -394,7 +416,7 @@ def peer_barrier(flag_ptrs, rank: int, epoch: int, device, max_polls: int | None
     ``max_polls`` (about 0.5 us each, at most 2**26) replaces the default bound of about a second."""
     lib = load_library()
     arr = _pointer_array(flag_ptrs)
-    with torch.cuda.device(device):
+    with _on_device(device):
         if max_polls is None:
             _check(lib.ck_peer_barrier(arr, rank, len(flag_ptrs), epoch & 0xFFFFFFFF, _stream(device)), "peer_barrier")
         else:
@@ -461,7 +483,7 @@ def linear_nvfp4_from_float(x: torch.Tensor, w_codes: torch.Tensor, w_scale: tor
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
         _linear_workspaces[key] = ws
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _check(lib.ck_linear_nvfp4_from_float(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(sx), _ptr(w_codes), _ptr(w_block_scales),
                                               _ptr(sw), bias_ptr, bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k,
                                               ws.data_ptr(), ws.numel(), _stream(dev)), "linear_nvfp4_from_float")
@@ -496,7 +518,7 @@ def linear_mxfp8_from_float(x: torch.Tensor, w_data: torch.Tensor, w_block_scale
         ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
         _linear_workspaces[key] = ws
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _check(lib.ck_linear_mxfp8_from_float(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(w_data), _ptr(w_block_scales), bias_ptr,
                                               bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, ws.data_ptr(),
                                               ws.numel(), _stream(dev)), "linear_mxfp8_from_float")
@@ -543,7 +565,7 @@ def linear_nvfp4_fused(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.T
         rq = _scalar_f32(requant_scale, dev, "requant_scale")
         codes = torch.empty((m, n // 2), dtype=torch.uint8, device=dev)
         scales = torch.empty((roundup(m, 128), n // 16), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _check(lib.ck_linear_nvfp4_fused(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), _ptr(tsa), _ptr(tsb),
                                          None, bias_ptr, bias_code, ACTIVATIONS[activation], _ptr(out),
                                          DTYPE_TO_CODE[out_dtype], _ptr(codes), _ptr(scales), _ptr(rq), m, n, k,
@@ -570,7 +592,7 @@ def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
     dev = a.device
     bias_ptr, bias_code, bias_keep = _bias_args(bias, n, dev)
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         ws_ptr, ws_bytes = _gemm_workspace(lib, True, m, n, k, dev)
         _check(lib.ck_scaled_mm_mxfp8_ws(_ptr(a), _ptr(b), _ptr(block_scale_a), _ptr(block_scale_b), bias_ptr, bias_code,
                                          _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, ws_ptr, ws_bytes, _stream(dev)),
