@@ -23,7 +23,7 @@ struct SmallPlan {
   int64_t partial_bytes;   // splits > 1: tiles x splits x 128 x tile_n floats
 };
 
-SmallPlan plan_small(int64_t M, int64_t N, int k_bytes) {
+SmallPlan plan_small(int64_t N, int k_bytes) {
   SmallPlan pl{};
   const int k_stages = static_cast<int>(ceil_div(k_bytes, kStageKBytes));
   const int64_t tiles = ceil_div(N, kTileM);
@@ -47,7 +47,7 @@ SmallPlan plan_small(int64_t M, int64_t N, int k_bytes) {
 }
 
 template <Kind KIND, typename OutT>
-int launch_small(const SmallPlan& pl, const Operands& ops, const GemmParams& p, cudaStream_t stream) {
+int launch_small(const Operands& ops, const GemmParams& p, cudaStream_t stream) {
   OutputSpec os;
   void* const single[1] = {p.out};
   os.ptrs = single;
@@ -63,7 +63,7 @@ bool small_m_applies(int64_t M, int64_t N, int64_t K) { return M >= 1 && M <= kM
 
 int64_t small_m_workspace_bytes(bool is_mxfp8, int64_t M, int64_t N, int64_t K) {
   if (!small_m_applies(M, N, K)) return 0;
-  const SmallPlan pl = plan_small(M, N, static_cast<int>(is_mxfp8 ? K : K / 2));
+  const SmallPlan pl = plan_small(N, static_cast<int>(is_mxfp8 ? K : K / 2));
   return pl.splits > 1 ? kWorkspaceTicketBytes + pl.partial_bytes : 0;
 }
 
@@ -90,7 +90,7 @@ int scaled_mm_small_m(bool is_mxfp8, const void* a, const void* b, const void* s
   p.n_row_blocks_a = static_cast<int>(ceil_div(N, 128));
   p.n_row_blocks_b = static_cast<int>(ceil_div(M, 128));
   if (int rc = gemm_status_word(&p.status)) return rc;
-  SmallPlan pl = plan_small(M, N, p.k_bytes);
+  SmallPlan pl = plan_small(N, p.k_bytes);
   const int64_t need = kWorkspaceTicketBytes + pl.partial_bytes;
   if (pl.splits > 1 && (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)) {
     pl.splits = 1;  // no (usable) workspace: one item per tile
@@ -105,15 +105,15 @@ int scaled_mm_small_m(bool is_mxfp8, const void* a, const void* b, const void* s
   const Operands ops = {b, a};
   if (is_mxfp8) {
     switch (out_dtype) {
-      case CK_DTYPE_BF16: return launch_small<Kind::kMxfp8, __nv_bfloat16>(pl, ops, p, stream);
-      case CK_DTYPE_F16: return launch_small<Kind::kMxfp8, __half>(pl, ops, p, stream);
-      default: return launch_small<Kind::kMxfp8, float>(pl, ops, p, stream);
+      case CK_DTYPE_BF16: return launch_small<Kind::kMxfp8, __nv_bfloat16>(ops, p, stream);
+      case CK_DTYPE_F16: return launch_small<Kind::kMxfp8, __half>(ops, p, stream);
+      default: return launch_small<Kind::kMxfp8, float>(ops, p, stream);
     }
   }
   switch (out_dtype) {
-    case CK_DTYPE_BF16: return launch_small<Kind::kNvfp4, __nv_bfloat16>(pl, ops, p, stream);
-    case CK_DTYPE_F16: return launch_small<Kind::kNvfp4, __half>(pl, ops, p, stream);
-    default: return launch_small<Kind::kNvfp4, float>(pl, ops, p, stream);
+    case CK_DTYPE_BF16: return launch_small<Kind::kNvfp4, __nv_bfloat16>(ops, p, stream);
+    case CK_DTYPE_F16: return launch_small<Kind::kNvfp4, __half>(ops, p, stream);
+    default: return launch_small<Kind::kNvfp4, float>(ops, p, stream);
   }
 }
 
