@@ -54,14 +54,6 @@ __device__ __forceinline__ void store16(OutT* dst, const float (&v)[16]) {
   }
 }
 
-__device__ __forceinline__ float e2m1_value(uint32_t code) {
-  // 0, .5, 1, 1.5, 2, 3, 4, 6 with the sign in bit 3 (-0 for code 8)
-  const uint32_t m = code & 7u;
-  const float mag = (m < 2u) ? 0.5f * static_cast<float>(m)
-                             : __uint_as_float(((m >> 1) + 126u) << 23 | ((m & 1u) << 22));
-  return (code & 8u) ? -mag : mag;
-}
-
 __device__ __forceinline__ float e4m3_byte_to_f32(uint32_t b) {
   uint32_t h2;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(b)));
