@@ -264,3 +264,31 @@ def test_nvfp4_mlp_fused_equals_the_unfused_layers(ck, cuda_device, rows):
     assert fused.shape == unfused.shape == (*x.shape[:-1], 256)
     assert torch.equal(fused, unfused)
     assert "fc2.input_scale" in mlp.state_dict()
+
+
+def test_layers_replay_from_a_cuda_graph(ck, cuda_device):
+    """The one-call paths of the layers and the fused MLP are launch-only: captured once, replayed on
+    new input values, same bits as the eager call."""
+    from comfy_kitchen.modules import MXFP8Linear, NVFP4Linear, NVFP4MLP
+
+    fc1 = NVFP4Linear.from_linear(_dense(cuda_device, 256, 512, seed=3))
+    fc2 = NVFP4Linear.from_linear(_dense(cuda_device, 512, 256, seed=4))
+    mlp = NVFP4MLP(fc1, fc2)
+    mx = MXFP8Linear.from_linear(_dense(cuda_device, 256, 384, seed=5))
+    x = torch.randn(160, 256, device=cuda_device, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        mlp.calibrate(x)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up on the capture stream: workspaces are per stream
+                mlp(x), fc1(x), mx(x)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                outs = (mlp(x), fc1(x), mx(x))
+        x.copy_(torch.randn(160, 256, device=cuda_device, dtype=torch.bfloat16))
+        graph.replay()
+        torch.cuda.synchronize()
+        want = (mlp(x), fc1(x), mx(x))
+    for got, ref in zip(outs, want):
+        assert torch.equal(got, ref)
