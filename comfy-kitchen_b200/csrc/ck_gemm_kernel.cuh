@@ -543,6 +543,10 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // second CTA of a pair: the leader issues the MMAs and the scale copies for both
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // Nothing can land before the producer's own dependency wait is over; waiting here too keeps
+    // the bounded barrier waits below from running (and giving up) while a long predecessor - a
+    // cross-GPU barrier that waits for a late rank, say - is still executing.
+    pdl_wait();
     // Descriptors differ between stages only in their start-address field, so the loop
     // carries 32-bit low words; the high words are constants.
     const uint32_t a_lo0 = static_cast<uint32_t>(make_operand_desc_sw128(smem_u32(smem_a)));
