@@ -21,7 +21,6 @@ from __future__ import annotations
 
 import argparse
 import ctypes
-import glob
 import os
 import subprocess
 import sys
