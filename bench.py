@@ -841,6 +841,28 @@ def run_gemm_sweep(args, torch, ck, device) -> dict:
             t = time_replays(torch, f, 20, 3, min_seconds=0.0, min_replays=11)
             us = t["median_ms"] / 20 * 1e3
             row = {"M": m, "N": n, "K": k, "us": us, "tflops": 2.0 * m * n * k / (us * 1e-6) / 1e12, "weight_copies": copies}
+            if not args.no_ref_kernels and qx.shape[0] == m:
+                # the same launches through cuBLASLt (torch.nn.functional.scaled_mm), same operands and harness
+                try:
+                    from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+                    f4, e4m3 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+                    recipe = [ScalingType.BlockWise1x16, ScalingType.TensorWise]
+                    swz = [SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE]
+                    qx4, bsx1 = qx.view(f4), bsx.view(e4m3).view(-1)
+                    qw4 = [q.view(f4).t() for q in qw]
+                    bsw1 = [b.view(e4m3).view(-1) for b in bsw]
+
+                    def g(i, st):
+                        j = i % copies
+                        return scaled_mm(qx4, qw4[j], scale_a=[bsx1, sx], scale_recipe_a=recipe, scale_b=[bsw1[j], sw],
+                                         scale_recipe_b=recipe, swizzle_a=swz, swizzle_b=swz, output_dtype=torch.bfloat16)
+
+                    same = bool(torch.equal(g(0, None), f(0, None)))
+                    tr = time_replays(torch, g, 20, 3, min_seconds=0.0, min_replays=11)
+                    row["cublaslt_us"] = tr["median_ms"] / 20 * 1e3
+                    row["cublaslt_bit_identical"] = same
+                except Exception as e:  # noqa: BLE001 - shapes the library refuses are reported, not fatal
+                    row["cublaslt_unavailable"] = f"{type(e).__name__}: {e}"[:120]
             if m <= 256:
                 by = 0.5625 * (m * k + n * k) + 2.0 * m * n
                 row.update({"bound": "hbm", "algorithmic_bytes": by, "gbs": by / (us * 1e-6) / 1e9,
