@@ -134,6 +134,7 @@ struct GemmParams {
   int n_row_blocks_a;      // ceil(M / 128)
   int n_row_blocks_b;      // ceil(N / 128)
   int tiles_m, tiles_n;
+  int raster;              // order in which workers walk the tiles: 0 = down the rows first, 1 = along the columns first
   int out_tma;             // the output qualifies for TMA stores (16-byte aligned base and pitch)
   int n_out;               // destinations of every output tile (1, or one per GPU of an all-gather)
   int splits;              // split-K: work items per tile (1 = off); item s of a tile covers pipeline stages
@@ -149,6 +150,14 @@ struct GemmParams {
   const float* rq_scale;   // its per-tensor scale (device)
 };
 
+
+// Tile index -> (row block, column block) in the walking order the launch chose.
+__device__ __forceinline__ int tile_row_block(const GemmParams& p, int tile) {
+  return p.raster == 0 ? tile % p.tiles_m : tile / p.tiles_n;
+}
+__device__ __forceinline__ int tile_col_block(const GemmParams& p, int tile) {
+  return p.raster == 0 ? tile / p.tiles_m : tile % p.tiles_n;
+}
 
 // Destinations of the output tile: one tensor map for a plain GEMM; for the column-sharded
 // GEMM with a fused all-gather, one per GPU - each a window [M, N_local] at this rank's column
@@ -396,8 +405,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int tile0 = worker / pf_splits;
       const int ks0 = (worker - tile0 * pf_splits) * p.k_stages_per_split;
       const int ks1 = min(min(pf_k_stages, ks0 + p.k_stages_per_split), ks0 + STAGES);
-      const int pm0 = (tile0 % p.tiles_m) * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM;
-      const int pn0 = (tile0 / p.tiles_m) * TILE_N + static_cast<int>(cta_rank) * Cfg::kBRows;
+      const int pm0 = tile_row_block(p, tile0) * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM;
+      const int pn0 = tile_col_block(p, tile0) * TILE_N + static_cast<int>(cta_rank) * Cfg::kBRows;
       for (int ks = ks0; ks < ks1; ++ks) {
         tma_prefetch_2d(&map_a, ks * kStageKBytes, pm0);
         tma_prefetch_2d(&map_b, ks * kStageKBytes, pn0);
@@ -475,8 +484,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
       const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
       // consecutive workers take tiles that share the B columns (tile_m fastest)
-      const int tile_m = tile % p.tiles_m;
-      const int tile_n = tile / p.tiles_m;
+      const int tile_m = tile_row_block(p, tile);
+      const int tile_n = tile_col_block(p, tile);
       const int m0 = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM;  // this CTA's rows of A
       const int n0 = tile_n * TILE_N;
       const int rb_b0 = n0 / 128;
@@ -569,7 +578,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int tile = item / splits;
       const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
       const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
-      const int n0 = (tile / p.tiles_m) * TILE_N;
+      const int n0 = tile_col_block(p, tile) * TILE_N;
       const int acc = tile_it % NUM_ACC;
       const uint32_t acc_ph = (tile_it / NUM_ACC) & 1;
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
@@ -673,8 +682,8 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     for (int item = worker; item < num_items; item += num_workers, ++tile_it) {
       const int tile = item / splits;
       const int split = item - tile * splits;
-      const int tile_m = tile % p.tiles_m;
-      const int tile_n = tile / p.tiles_m;
+      const int tile_m = tile_row_block(p, tile);
+      const int tile_n = tile_col_block(p, tile);
       const int row = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM + quarter * 32 + lane;
       const int n0 = tile_n * TILE_N;
       const int acc = tile_it % NUM_ACC;
@@ -791,7 +800,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const bool has_next = next_item < num_items;
       float bias_prefetched = 0.0f;
       if (has_next && et < TILE_N) {
-        const int n = ((next_item / splits) / p.tiles_m) * TILE_N + et;
+        const int n = tile_col_block(p, next_item / splits) * TILE_N + et;
         if (with_bias && n < p.N) bias_prefetched = load_bias(p.bias, p.bias_dtype, n);
       }
       if (warp == 2) CK_TRACE(6);
@@ -1265,6 +1274,17 @@ int launch_config(const Operands& ops, GemmParams p, const OutputSpec& os, cudaS
   if (CTAS == 2) {
     if (int rc = make_scale_map(&map_sfa, p.sfa, p.n_row_blocks_a, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
     if (int rc = make_scale_map(&map_sfb, p.sfb, p.n_row_blocks_b, p.sf_col_tiles, Cfg::kSfTilesPerStage)) return rc;
+  }
+  // Walking order of the tiles: the one whose concurrently running tiles touch fewer operand bytes
+  // (A row blocks + B column blocks of one wave), so that a long operand is not pulled through L2
+  // once per tile column (M = 16384, K = 12288: 100 MB of A per wave down the rows, 28 MB along the
+  // columns).
+  if (!SWAP) {
+    const int64_t a_block = static_cast<int64_t>(Cfg::kTileRows) * p.k_bytes, b_block = static_cast<int64_t>(TILE_N) * p.k_bytes;
+    const int64_t w = workers, tm = p.tiles_m, tn = p.tiles_n;
+    const int64_t down = (w < tm ? w : tm) * a_block + ceil_div(w, tm) * b_block;
+    const int64_t along = ceil_div(w, tn) * a_block + (w < tn ? w : tn) * b_block;
+    p.raster = along < down ? 1 : 0;
   }
   OutputMaps maps_out = {};
   p.out_tma = 0;
