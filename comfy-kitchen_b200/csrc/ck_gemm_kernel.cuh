@@ -483,7 +483,7 @@ block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int tile = item / splits;
       const int ks_begin = (item - tile * splits) * p.k_stages_per_split;
       const int ks_end = min(k_stages, ks_begin + p.k_stages_per_split);
-      // consecutive workers take tiles that share the B columns (tile_m fastest)
+      // consecutive workers take neighbouring tiles in the walking order the launch chose (p.raster)
       const int tile_m = tile_row_block(p, tile);
       const int tile_n = tile_col_block(p, tile);
       const int m0 = tile_m * Cfg::kTileRows + static_cast<int>(cta_rank) * kTileM;  // this CTA's rows of A
